@@ -1,0 +1,127 @@
+// Shared helpers for the trittention kernels: dtype conversion, error reporting,
+// the attention-mask predicates, and launch-argument bundles.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/tritt.h"
+
+namespace tritt {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// ---------------------------------------------------------------- error reporting
+void set_error(const char* fmt, ...);
+const char* get_error();
+
+#define TRITT_CUDA_OK(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess) {                                                             \
+      ::tritt::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+      return (int)_e;                                                                    \
+    }                                                                                    \
+  } while (0)
+
+// ---------------------------------------------------------------- dtype helpers
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float silu_grad_f(float x) {
+  float s = 1.f / (1.f + __expf(-x));
+  return s * (1.f + x * (1.f - s));
+}
+
+inline size_t dtype_size(int dtype) { return dtype == TRITT_F32 ? 4 : 2; }
+
+// ---------------------------------------------------------------- masks
+// Triple-dot-product mask (reference triple_dot_product/kernels/utils.py:75-90 and
+// trittention_pytorch.py:68-75): (q, j, k) is attended iff
+//   j <= q <= j + k1w,  k <= q <= k + k2w,  k - kkl <= j <= k + kkr     (causal)
+// and always when not causal.  Windows are normalised on the host so that
+// "unlimited" equals T.
+struct TdpMask {
+  int causal, T, k1w, k2w, kkl, kkr;
+  __host__ __device__ bool valid(int q, int j, int k) const {
+    if (!causal) return true;
+    return j <= q && q - j <= k1w && k <= q && q - k <= k2w && k - j <= kkl && j - k <= kkr;
+  }
+  // full windows: the mask is the plain "j <= q and k <= q" wedge
+  __host__ __device__ bool full_windows() const {
+    return !causal || (k1w >= T - 1 && k2w >= T - 1 && kkl >= T - 1 && kkr >= T - 1);
+  }
+};
+
+inline TdpMask make_tdp_mask(int causal, int T, int k1w, int k2w, int kkl, int kkr) {
+  auto norm = [T](int w) { return (w < 0 || w > T) ? T : w; };
+  return TdpMask{causal ? 1 : 0, T, norm(k1w), norm(k2w), norm(kkl), norm(kkr)};
+}
+
+// ---------------------------------------------------------------- argument bundle
+struct TdpArgs {
+  const void *q, *k1, *k2, *v1, *v2, *o, *d_o;
+  const float* lse_in;  // backward: saved log-sum-exp
+  void *out_o;          // forward output
+  float* out_lse;
+  void *dq, *dk1, *dk2, *dv1, *dv2;
+  int B, N, T, D, dtype;
+  float alpha;
+  TdpMask mask;
+  int q_mod, q_rem;
+  void* workspace;
+  size_t workspace_bytes;
+  int* status_word;
+  int flags;
+  cudaStream_t stream;
+};
+
+struct DpsArgs {
+  const void *q, *k1, *k2, *v1, *v2, *o, *d_o;
+  const float* m_in;
+  void* out_o;
+  float* out_m;
+  void *dq, *dk1, *dk2, *dv1, *dv2;
+  int B, N, T, D, dtype;
+  float alpha;
+  int causal, k_diff;
+  void* workspace;
+  size_t workspace_bytes;
+  int* status_word;
+  int flags;
+  cudaStream_t stream;
+};
+
+// kernel families (defined in their own translation units)
+int simt_tdp_fwd(const TdpArgs& a);
+int simt_tdp_bwd(const TdpArgs& a);
+int simt_tdp_bwd_finalize(const void* v1, void* dk1, void* dk2, void* dv1, void* dv2, size_t n_elems, int dtype,
+                          const float* partials, cudaStream_t stream);
+size_t simt_tdp_workspace(int op, int B, int N, int T, int D, int dtype);
+
+int simt_dps_fwd(const DpsArgs& a);
+int simt_dps_bwd(const DpsArgs& a);
+size_t simt_dps_workspace(int op, int B, int N, int T, int D, int dtype);
+
+bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m);
+int sm100_tdp_fwd(const TdpArgs& a);
+int sm100_tdp_bwd(const TdpArgs& a);
+size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype);
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace tritt

@@ -1,0 +1,200 @@
+"""ctypes binding of ``libtritt_sm100.so`` (declared in ``include/tritt.h``).
+
+The library is the only compute path: if it is missing, loading raises and every entry
+point of the package fails loudly.  There is no PyTorch or CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtritt_sm100.so")
+
+F32, F16, BF16 = 0, 1, 2
+OP_TDP_FWD, OP_TDP_BWD, OP_DPS_FWD, OP_DPS_BWD = 0, 1, 2, 3
+FLAG_FORCE_SIMT, FLAG_BWD_PARTIAL = 1, 2
+PATH_SIMT, PATH_TCGEN05 = 0, 1
+
+_DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+# every symbol include/tritt.h declares
+SYMBOLS = (
+    "tritt_version", "tritt_last_error", "tritt_workspace_bytes", "tritt_tdp_path", "tritt_tdp_fwd",
+    "tritt_tdp_bwd", "tritt_tdp_bwd_finalize", "tritt_tdp_bwd_partials_offset", "tritt_dps_fwd",
+    "tritt_dps_bwd", "tritt_selftest_umma",
+)
+
+_lib = None
+_lock = threading.Lock()
+_status = {}
+launches = 0  # kernels-enqueuing library calls made by this process (bench bookkeeping)
+
+
+class TrittError(RuntimeError):
+    pass
+
+
+def lib():
+    """Loads the shared library on first use."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise TrittError(
+                        f"{LIB_PATH} not found: build it with `python flash-3-way-attention_b200/build.py` "
+                        "(there is no fallback path)")
+                L = C.CDLL(LIB_PATH)
+                vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+                L.tritt_version.restype = i
+                L.tritt_last_error.restype = C.c_char_p
+                L.tritt_workspace_bytes.restype = sz
+                L.tritt_workspace_bytes.argtypes = [i] * 6
+                L.tritt_tdp_path.restype = i
+                L.tritt_tdp_path.argtypes = [i] * 10
+                L.tritt_tdp_bwd_partials_offset.restype = sz
+                L.tritt_tdp_bwd_partials_offset.argtypes = [i] * 5
+                L.tritt_tdp_fwd.restype = i
+                L.tritt_tdp_fwd.argtypes = [vp] * 7 + [i] * 5 + [f] + [i] * 7 + [vp, sz, vp, i, vp]
+                L.tritt_tdp_bwd.restype = i
+                L.tritt_tdp_bwd.argtypes = [vp] * 13 + [i] * 5 + [f] + [i] * 7 + [vp, sz, vp, i, vp]
+                L.tritt_tdp_bwd_finalize.restype = i
+                L.tritt_tdp_bwd_finalize.argtypes = [vp] * 5 + [i] * 5 + [vp, sz, vp]
+                L.tritt_dps_fwd.restype = i
+                L.tritt_dps_fwd.argtypes = [vp] * 7 + [i] * 5 + [f] + [i] * 2 + [vp, sz, vp, i, vp]
+                L.tritt_dps_bwd.restype = i
+                L.tritt_dps_bwd.argtypes = [vp] * 13 + [i] * 5 + [f] + [i] * 2 + [vp, sz, vp, i, vp]
+                L.tritt_selftest_umma.restype = i
+                L.tritt_selftest_umma.argtypes = [vp] * 5 + [i, vp, vp]
+                _lib = L
+    return _lib
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPES[dt]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {dt}: expected float32, float16 or bfloat16") from None
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        msg = lib().tritt_last_error().decode("utf-8", "replace")
+        if rc < 0:
+            raise ValueError(f"{what}: {msg} (code {rc})")
+        raise TrittError(f"{what}: {msg} (CUDA error {rc})")
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 that kernels OR a code into when a bounded barrier wait ran out."""
+    key = torch.device(device).index
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = t
+    return t
+
+
+def read_status(device) -> int:
+    """Synchronises and returns (then clears) the device's kernel status word."""
+    t = status_word(device)
+    v = int(t.item())
+    if v:
+        t.zero_()
+    return v
+
+
+def workspace(op: int, B: int, N: int, T: int, D: int, dtype: int, device) -> torch.Tensor:
+    nbytes = lib().tritt_workspace_bytes(op, B, N, T, D, dtype)
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _win(w, T):
+    return T if w is None else int(w)
+
+
+def tdp_path(op, T, D, dtype, causal, k1w, k2w, kkl, kkr, flags=0) -> int:
+    return lib().tritt_tdp_path(op, T, D, dtype, int(bool(causal)), _win(k1w, T), _win(k2w, T), _win(kkl, T),
+                                _win(kkr, T), flags)
+
+
+def tdp_fwd(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr, q_mod=1, q_rem=0, flags=0):
+    global launches
+    B, N, T, D = q.shape
+    dt = dtype_code(q.dtype)
+    with torch.cuda.device(q.device):
+        ws = workspace(OP_TDP_FWD, B, N, T, D, dt, q.device)
+        rc = lib().tritt_tdp_fwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
+                                 o.data_ptr(), lse.data_ptr(), B, N, T, D, dt, float(alpha), int(bool(causal)),
+                                 _win(k1w, T), _win(k2w, T), _win(kkl, T), _win(kkr, T), q_mod, q_rem,
+                                 ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), flags, _stream())
+    _check(rc, "tritt_tdp_fwd")
+    launches += 1
+
+
+def tdp_bwd(q, k1, k2, v1, v2, o, do, lse, dq, dk1, dk2, dv1, dv2, alpha, causal, k1w, k2w, kkl, kkr,
+            q_mod=1, q_rem=0, flags=0, ws=None):
+    """Returns the workspace tensor (holds the fp32 partial sums when FLAG_BWD_PARTIAL is set)."""
+    global launches
+    B, N, T, D = q.shape
+    dt = dtype_code(q.dtype)
+    ptr = lambda t: 0 if t is None else t.data_ptr()
+    with torch.cuda.device(q.device):
+        if ws is None:
+            ws = workspace(OP_TDP_BWD, B, N, T, D, dt, q.device)
+        rc = lib().tritt_tdp_bwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
+                                 o.data_ptr(), do.data_ptr(), lse.data_ptr(), dq.data_ptr(), ptr(dk1), ptr(dk2),
+                                 ptr(dv1), ptr(dv2), B, N, T, D, dt, float(alpha), int(bool(causal)),
+                                 _win(k1w, T), _win(k2w, T), _win(kkl, T), _win(kkr, T), q_mod, q_rem,
+                                 ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), flags, _stream())
+    _check(rc, "tritt_tdp_bwd")
+    launches += 1
+    return ws
+
+
+def tdp_bwd_finalize(v1, dk1, dk2, dv1, dv2, ws):
+    global launches
+    B, N, T, D = v1.shape
+    with torch.cuda.device(v1.device):
+        rc = lib().tritt_tdp_bwd_finalize(v1.data_ptr(), dk1.data_ptr(), dk2.data_ptr(), dv1.data_ptr(),
+                                          dv2.data_ptr(), B, N, T, D, dtype_code(v1.dtype), ws.data_ptr(),
+                                          ws.numel(), _stream())
+    _check(rc, "tritt_tdp_bwd_finalize")
+    launches += 1
+
+
+def dps_fwd(q, k1, k2, v1, v2, o, m, alpha, causal, k_diff, flags=0):
+    global launches
+    B, N, T, D = q.shape
+    dt = dtype_code(q.dtype)
+    with torch.cuda.device(q.device):
+        ws = workspace(OP_DPS_FWD, B, N, T, D, dt, q.device)
+        rc = lib().tritt_dps_fwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
+                                 o.data_ptr(), m.data_ptr(), B, N, T, D, dt, float(alpha), int(bool(causal)),
+                                 int(k_diff), ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), flags,
+                                 _stream())
+    _check(rc, "tritt_dps_fwd")
+    launches += 1
+
+
+def dps_bwd(q, k1, k2, v1, v2, o, do, m, dq, dk1, dk2, dv1, dv2, alpha, causal, k_diff, flags=0):
+    global launches
+    B, N, T, D = q.shape
+    dt = dtype_code(q.dtype)
+    with torch.cuda.device(q.device):
+        ws = workspace(OP_DPS_BWD, B, N, T, D, dt, q.device)
+        rc = lib().tritt_dps_bwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
+                                 o.data_ptr(), do.data_ptr(), m.data_ptr(), dq.data_ptr(), dk1.data_ptr(),
+                                 dk2.data_ptr(), dv1.data_ptr(), dv2.data_ptr(), B, N, T, D, dt, float(alpha),
+                                 int(bool(causal)), int(k_diff), ws.data_ptr(), ws.numel(),
+                                 status_word(q.device).data_ptr(), flags, _stream())
+    _check(rc, "tritt_dps_bwd")
+    launches += 1

@@ -1,0 +1,132 @@
+/*
+ * tritt.h - C ABI of libtritt_sm100.so: three-way ("trittention") attention for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The library replaces the device side of the reference package flash_trittention
+ * (Triton kernels launched from Python); each entry point below names the reference
+ * launch site it stands in for.  Host glue (argument validation, torch.autograd
+ * plumbing) lives above this ABI and mirrors the reference's Python modules.
+ *
+ * Conventions
+ *   - every tensor is row-major [B, N, T, D], innermost stride 1, base pointer 16-byte
+ *     aligned, all of one dtype (TRITT_F32 / TRITT_F16 / TRITT_BF16); lse / m vectors
+ *     are fp32 [B, N, T] holding the natural-log log-sum-exp of the scaled logits;
+ *   - pointers are DEVICE pointers; the caller owns every buffer including `workspace`
+ *     and keeps them alive until the work enqueued on `stream` has run;
+ *   - calls only enqueue work on `stream` (no synchronisation, no device allocation);
+ *   - return value 0 = success, negative = invalid argument, positive = cudaError_t of
+ *     a failed runtime call.  tritt_last_error() gives a thread-local message;
+ *   - `status_word` (device int, may be NULL) is OR-ed with a non-zero code by a kernel
+ *     whose bounded barrier wait ran out; the caller zeroes and reads it;
+ *   - window arguments follow the reference: a value >= T (or < 0) means "unlimited".
+ */
+#ifndef TRITT_H_
+#define TRITT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* tritt_stream_t; /* a cudaStream_t / CUstream */
+
+enum { TRITT_F32 = 0, TRITT_F16 = 1, TRITT_BF16 = 2 };
+
+/* operations, for tritt_workspace_bytes() */
+enum { TRITT_OP_TDP_FWD = 0, TRITT_OP_TDP_BWD = 1, TRITT_OP_DPS_FWD = 2, TRITT_OP_DPS_BWD = 3 };
+
+/* flags */
+enum {
+  TRITT_FLAG_FORCE_SIMT = 1,  /* use the plain fp32 CUDA-core kernels even where the tensor-core path applies */
+  TRITT_FLAG_BWD_PARTIAL = 2  /* tritt_tdp_bwd: leave the fp32 key-side partial sums in the workspace and do not
+                                 write dk1/dk2/dv1/dv2 (the caller reduces them across ranks, then calls
+                                 tritt_tdp_bwd_finalize) */
+};
+
+/* kernel families, as reported by tritt_tdp_path() */
+enum { TRITT_PATH_SIMT = 0, TRITT_PATH_TCGEN05 = 1 };
+
+int tritt_version(void);
+const char* tritt_last_error(void);
+
+/* Bytes of caller-provided scratch the given operation needs (0 if none). */
+size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype);
+
+/* Which kernel family a TDP call with these arguments runs on. */
+int tritt_tdp_path(int op, int T, int D, int dtype, int causal, int k1_window, int k2_window, int kk_left,
+                   int kk_right, int flags);
+
+/*
+ * Triple-dot-product forward.  Replaces the launch of `_tritt_fwd` and the host-side
+ * SiLU / `M + log(L)` passes around it in the reference
+ * (src/flash_trittention/triple_dot_product/flash_trittention.py:61-62,92-128).
+ *   S[q,j,k] = alpha * sum_h q[q,h] k1[j,h] k2[k,h];  softmax over the attended (j,k);
+ *   o[q,h]   = sum_jk P[q,j,k] SiLU(v1[j,h]) v2[k,h];  lse[q] = log sum_jk exp(S).
+ * (q_mod, q_rem): only query rows q with q % q_mod == q_rem are computed and written
+ * (query-row sharding across devices); pass (1, 0) for all rows.
+ */
+int tritt_tdp_fwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, void* o,
+                  float* lse, int B, int N, int T, int D, int dtype, float alpha, int causal, int k1_window,
+                  int k2_window, int kk_left, int kk_right, int q_mod, int q_rem, void* workspace,
+                  size_t workspace_bytes, int* status_word, int flags, tritt_stream_t stream);
+
+/*
+ * Triple-dot-product backward.  Replaces the five launches `_tritt_bwd_dq/_dk1/_dk2/_dv1/_dv2`
+ * and the host-side SiLU, D = sum(dO*O), zero-init and SiLU' passes of the reference
+ * (src/flash_trittention/triple_dot_product/flash_trittention.py:158-173,191-391).
+ * v1 is the RAW (pre-SiLU) tensor; dv1 is the gradient w.r.t. it.  With (q_mod, q_rem) != (1, 0)
+ * only the selected rows of dq are written and the key-side gradients are partial sums.
+ */
+int tritt_tdp_bwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, const void* o,
+                  const void* d_o, const float* lse, void* dq, void* dk1, void* dk2, void* dv1, void* dv2, int B,
+                  int N, int T, int D, int dtype, float alpha, int causal, int k1_window, int k2_window,
+                  int kk_left, int kk_right, int q_mod, int q_rem, void* workspace, size_t workspace_bytes,
+                  int* status_word, int flags, tritt_stream_t stream);
+
+/*
+ * Second half of a TRITT_FLAG_BWD_PARTIAL backward: converts the fp32 partial sums
+ * (workspace layout: dK1 | dK2 | dSiLU(V1) | dV2, each [B,N,T,D] fp32, starting at
+ * tritt_tdp_bwd_partials_offset() bytes) to the output dtype and applies SiLU'(v1) to dv1
+ * (reference flash_trittention.py:390-391).  No counterpart launch in the reference: the
+ * reference has no multi-device path.
+ */
+int tritt_tdp_bwd_finalize(const void* v1, void* dk1, void* dk2, void* dv1, void* dv2, int B, int N, int T, int D,
+                           int dtype, void* workspace, size_t workspace_bytes, tritt_stream_t stream);
+size_t tritt_tdp_bwd_partials_offset(int B, int N, int T, int D, int dtype);
+
+/*
+ * Dot-product-sum forward.  Replaces the launch of the reference's `_tritt_fwd`
+ * (src/flash_trittention/dot_product_sum/trittention_triton.py:90-120).
+ *   S[q,s,t] = alpha * (q[q].k2[t] + k1[s].k2[t]);  causal: s <= t <= q and t - s <= k_diff;
+ *   o[q,h]   = sum_st P[q,s,t] SiLU(v1[s,h]) v2[t,h];  m[q] = log sum_st exp(S).
+ */
+int tritt_dps_fwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, void* o, float* m,
+                  int B, int N, int T, int D, int dtype, float alpha, int causal, int k_diff, void* workspace,
+                  size_t workspace_bytes, int* status_word, int flags, tritt_stream_t stream);
+
+/*
+ * Dot-product-sum backward.  Replaces `_tritt_bwd_preprocess`, `_tritt_bwd_dq`, `_tritt_bwd_dk_dv`
+ * and the host-side SiLU / SiLU' / dk2 merge passes of the reference
+ * (src/flash_trittention/dot_product_sum/trittention_triton.py:160,183-356).
+ */
+int tritt_dps_bwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, const void* o,
+                  const void* d_o, const float* m, void* dq, void* dk1, void* dk2, void* dv1, void* dv2, int B,
+                  int N, int T, int D, int dtype, float alpha, int causal, int k_diff, void* workspace,
+                  size_t workspace_bytes, int* status_word, int flags, tritt_stream_t stream);
+
+/*
+ * Self-test of the tensor-core building blocks (TMA tile loads, shared-memory operand
+ * descriptors, a 16-bit operand held in tensor memory): one CTA computes
+ *   C = A * Bm^T   and   C2 = round16(C) * V      (all matrices 128 x 128, row-major)
+ * so that a host test can compare against a plain matmul.  No counterpart in the
+ * reference (its kernels are Triton; the compiler picks the matrix instructions).
+ */
+int tritt_selftest_umma(const void* A, const void* Bm, const void* V, float* C, float* C2, int dtype,
+                        int* status_word, tritt_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRITT_H_ */
