@@ -121,6 +121,7 @@ bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m);
 int sm100_tdp_fwd(const TdpArgs& a);
 int sm100_tdp_bwd(const TdpArgs& a);
 size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype);
+size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D);
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

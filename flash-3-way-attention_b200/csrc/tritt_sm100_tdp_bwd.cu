@@ -1,0 +1,492 @@
+// Triple-dot-product trittention backward on Blackwell tensor cores (tcgen05 + TMEM + TMA).
+//
+// Same pair-row formulation as the forward kernel.  For one query q and a tile of 128 rows
+// x of a "row" key tensor X (with its value tensor Y), against 64-row slabs of the
+// "column" key/value tensors Kc / Vc:
+//     A [r,h] = alpha*log2(e) * Q[q,h]  * X[x_r,h]          A'[r,h] = dO[q,h] * Y[x_r,h]
+//     S  = A  Kc^T          P  = exp2(S - lse2[q])          (recomputed from the saved lse)
+//     dP = A' Vc^T          dS = P * (dP - Dq),  Dq = sum_h dO[q,h] O[q,h]
+//     G += dS Kc            U += P Vc                        (accumulated over the slabs in TMEM)
+// and per tile   dX[x_r,h] += alpha G[r,h] Q[q,h],   dY[x_r,h] += U[r,h] dO[q,h],
+//                dQ[q,h]   += alpha sum_r G[r,h] X[x_r,h].
+// Role 0 takes X = K2, Y = V2, Kc = K1, Vc = SiLU(V1) and yields dQ, dK2, dV2.  Role 1 swaps
+// the two key axes (the score and the gated value are symmetric under the swap): X = K1,
+// Y = SiLU(V1), Kc = K2, Vc = V2, and yields dK1 and dSiLU(V1).  Four GEMM-shaped products per
+// (tile, slab) and role - eight in all against the six of a minimal schedule - but every
+// key-side gradient is owned by rows of a tile, so the only cross-CTA reductions are
+// vector float adds of one 128 x D block per tile into fp32 accumulators.
+// (The reference runs one Triton kernel per gradient, recomputing P five times:
+// triple_dot_product/kernels/bwd_dq.py, bwd_dk1.py, bwd_dk2.py, bwd_dv1.py, bwd_dv2.py.)
+//
+// CTA layout (persistent, 256 threads): warp 0 TMA producer, warp 1 tcgen05.mma issuer,
+// warps 4-7 one warpgroup that forms the operands, turns (S, dP) into (P, dS) slab by slab
+// and folds G / U into the gradients.  Work item = (query, head, role); it walks the row
+// tiles x <= q and, inside, the column slabs c <= q.
+#include "tritt_sm100_tdp.cuh"
+
+#include <type_traits>
+
+namespace tritt {
+namespace {
+using namespace sm100;
+
+constexpr int kBwdThreads = 256;
+constexpr int kBC = 64;  // key columns per slab
+
+template <int D> struct BwdCfg {
+  static constexpr int kTileA = 128 * D * 2;
+  static constexpr int kStage = kBC * D * 2;
+  static constexpr int kStages = 8;
+  static constexpr int kOffA = 0;                  // A  (row-key pre-product)
+  static constexpr int kOffA2 = kTileA;            // A' (row-value pre-product)
+  static constexpr int kOffRing = 2 * kTileA;
+  static constexpr int kOffRed = kOffRing + kStages * kStage;  // [4][D] fp32 cross-warp sums
+  static constexpr int kOffVec = kOffRed + 4 * D * 4;          // [2][D] fp32: Q[q], dO[q]
+  static constexpr int kSmem = kOffVec + 2 * D * 4 + 1024;
+  static constexpr int kTmemS = 0, kTmemDP = 128, kTmemG = 256, kTmemU = 256 + D;
+};
+
+struct BwdParams {
+  const void *q, *o, *d_o;
+  const void *x[2], *y[2];  // row key / value tensors per role (raw pointers, for the epilogue)
+  const float* lse;
+  void* dq;
+  float *dX[2], *dY[2];     // fp32 accumulators per role
+  int T, BN, nq, q_mod, q_rem, causal;
+  float alpha;
+  int* status;
+};
+
+struct BwdBarriers {
+  uint64_t ring_full[8], ring_empty[8];
+  uint64_t xy_full, a_ready, a_free, gu_done;
+  uint64_t sdp_ready[2], pds_ready[2], wg_sync;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <int D, typename T16>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__ CUtensorMap tmK2,
+               const __grid_constant__ CUtensorMap tmSV1, const __grid_constant__ CUtensorMap tmV2,
+               const __grid_constant__ CUtensorMap tmK1r, const __grid_constant__ CUtensorMap tmK2r,
+               const __grid_constant__ CUtensorMap tmSV1r, const __grid_constant__ CUtensorMap tmV2r, BwdParams p) {
+  using Cfg = BwdCfg<D>;
+  constexpr int NS = Cfg::kStages;
+  constexpr int KH = D / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ BwdBarriers bars;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    bars.abort_flag = 0;
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&bars.ring_full[i], 1);
+      mbar_init(&bars.ring_empty[i], 1);
+    }
+    mbar_init(&bars.xy_full, 1);
+    mbar_init(&bars.a_ready, 128);
+    mbar_init(&bars.a_free, 128);
+    mbar_init(&bars.gu_done, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars.sdp_ready[b], 1);
+      mbar_init(&bars.pds_ready[b], 128);
+    }
+    mbar_init(&bars.wg_sync, 128);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&bars.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars.tmem_base;
+  volatile int* abort_flag = &bars.abort_flag;
+
+  const int T = p.T;
+  const long n_items = (long)p.nq * p.BN * 2;
+
+  // item -> (role, head, query); late (expensive) queries first
+  auto decode = [&](long item, int& role, int& bh, int& q) {
+    role = (int)(item & 1);
+    const long r = item >> 1;
+    bh = (int)(r % p.BN);
+    q = p.q_rem + (p.nq - 1 - (int)(r / p.BN)) * p.q_mod;
+  };
+  auto tile_counts = [&](int q, int& nxt, int& ncs) {
+    nxt = p.causal ? q / 128 + 1 : (T + 127) / 128;
+    ncs = p.causal ? q / kBC + 1 : (T + kBC - 1) / kBC;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const CUtensorMap* maps[8] = {&tmK1, &tmK2, &tmSV1, &tmV2, &tmK1r, &tmK2r, &tmSV1r, &tmV2r};
+      for (int i = 0; i < 8; ++i) tma_prefetch_desc(maps[i]);
+      uint32_t xt_count = 0, pos = 0;
+      bool alive = true;
+      auto load_stage = [&](const CUtensorMap* tm, int row0, int bh) -> bool {
+        const int st = pos % NS;
+        if (!mbar_wait(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag)) return false;
+        mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kStage);
+        for (int hh = 0; hh < KH; ++hh)
+          tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kStage + hh * (kBC * 128), tm, &bars.ring_full[st], hh * 64,
+                      row0, bh);
+        ++pos;
+        return true;
+      };
+      for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+        int role, bh, q, nxt, ncs;
+        decode(item, role, bh, q);
+        tile_counts(q, nxt, ncs);
+        // role 0: columns K1 / SiLU(V1), rows K2 / V2;   role 1: columns K2 / V2, rows K1 / SiLU(V1)
+        const CUtensorMap* tmKc = role == 0 ? &tmK1 : &tmK2;
+        const CUtensorMap* tmVc = role == 0 ? &tmSV1 : &tmV2;
+        const CUtensorMap* tmX = role == 0 ? &tmK2r : &tmK1r;
+        const CUtensorMap* tmY = role == 0 ? &tmV2r : &tmSV1r;
+        for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
+          if (!mbar_wait(&bars.a_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+          mbar_arrive_expect_tx(&bars.xy_full, 2 * Cfg::kTileA);
+          for (int hh = 0; hh < KH; ++hh) {
+            tma_load_3d(smem + Cfg::kOffA + hh * 16384, tmX, &bars.xy_full, hh * 64, xt * 128, bh);
+            tma_load_3d(smem + Cfg::kOffA2 + hh * 16384, tmY, &bars.xy_full, hh * 64, xt * 128, bh);
+          }
+          for (int c = 0; c < ncs && alive; ++c) {
+            alive = load_stage(tmKc, c * kBC, bh);
+            if (alive) alive = load_stage(tmVc, c * kBC, bh);
+          }
+        }
+      }
+      if (!alive) {
+        const uint32_t first = pos > (uint32_t)NS ? pos - NS : 0;
+        for (uint32_t q2 = first; q2 < pos; ++q2) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&bars.ring_full[q2 % NS], (q2 / NS) & 1) && clock64() - t0 < kWaitTicks / 8) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr int kFmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_s = make_idesc_f16(128, kBC, kFmt, false, false);
+      constexpr uint32_t idesc_g = make_idesc_f16(128, D, kFmt, false, true);
+      const uint32_t sA = smem_u32(smem + Cfg::kOffA), sA2 = smem_u32(smem + Cfg::kOffA2);
+      const uint32_t sRing = smem_u32(smem + Cfg::kOffRing);
+      uint32_t xt_count = 0, base = 0, n = 0;
+      bool alive = true;
+      auto wait_full = [&](uint32_t pos) { return mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag); };
+      // S(slab) = A Kc^T and dP(slab) = A' Vc^T
+      auto issue_sdp = [&](uint32_t slab_n, uint32_t pos) -> bool {
+        const uint32_t b = slab_n & 1;
+        if (!wait_full(pos)) return false;
+        {
+          const uint32_t st = pos % NS;
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint64_t da = make_smem_desc(sA + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+            const uint64_t db = make_smem_desc(sRing + st * Cfg::kStage + (k >> 2) * (kBC * 128) + (k & 3) * 32, 16, 1024);
+            mma_ss(tmem + Cfg::kTmemS + b * kBC, da, db, idesc_s, k > 0);
+          }
+        }
+        if (!wait_full(pos + 1)) return false;
+        {
+          const uint32_t st = (pos + 1) % NS;
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint64_t da = make_smem_desc(sA2 + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+            const uint64_t db = make_smem_desc(sRing + st * Cfg::kStage + (k >> 2) * (kBC * 128) + (k & 3) * 32, 16, 1024);
+            mma_ss(tmem + Cfg::kTmemDP + b * kBC, da, db, idesc_s, k > 0);
+          }
+        }
+        mma_commit(&bars.sdp_ready[b]);
+        return true;
+      };
+      // G (+)= dS Kc and U (+)= P Vc, then hand the two ring stages back
+      auto issue_gu = [&](uint32_t slab_n, uint32_t pos, bool accumulate) {
+        const uint32_t b = slab_n & 1;
+        const uint32_t stK = pos % NS, stV = (pos + 1) % NS;
+#pragma unroll
+        for (int k = 0; k < kBC / 16; ++k) {
+          const uint64_t db = make_smem_desc(sRing + stK * Cfg::kStage + k * 2048, kBC * 128, 1024);
+          mma_ts(tmem + Cfg::kTmemG, tmem + Cfg::kTmemDP + b * kBC + k * 8, db, idesc_g, accumulate || k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < kBC / 16; ++k) {
+          const uint64_t db = make_smem_desc(sRing + stV * Cfg::kStage + k * 2048, kBC * 128, 1024);
+          mma_ts(tmem + Cfg::kTmemU, tmem + Cfg::kTmemS + b * kBC + k * 8, db, idesc_g, accumulate || k > 0);
+        }
+        mma_commit(&bars.ring_empty[stK]);
+        mma_commit(&bars.ring_empty[stV]);
+      };
+
+      for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+        int role, bh, q, nxt, ncs;
+        decode(item, role, bh, q);
+        tile_counts(q, nxt, ncs);
+        for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
+          if (!mbar_wait(&bars.a_ready, xt_count & 1, abort_flag)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t n0 = n;
+          if (!issue_sdp(n0, base)) { alive = false; break; }
+          if (ncs > 1 && !issue_sdp(n0 + 1, base + 2)) { alive = false; break; }
+          for (int c = 0; c < ncs && alive; ++c) {
+            const uint32_t sn = n0 + c;
+            if (!mbar_wait(&bars.pds_ready[sn & 1], (sn >> 1) & 1, abort_flag)) { alive = false; break; }
+            tc_fence_after();
+            issue_gu(sn, base + 2 * c, c > 0);
+            if (c + 2 < ncs) {
+              if (!issue_sdp(sn + 2, base + 2 * (c + 2))) { alive = false; break; }
+            }
+          }
+          if (alive) mma_commit(&bars.gu_done);
+          n = n0 + ncs;
+          base += 2 * ncs;
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ soft-max / gradient warpgroup
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+    float* red = (float*)(smem + Cfg::kOffRed);
+    float* qv = (float*)(smem + Cfg::kOffVec);  // Q[q, :]
+    float* dov = qv + D;                        // dO[q, :]
+    uint32_t xt_count = 0, n = 0, wg_phase = 0;
+    bool alive = true;
+    auto wg_sync = [&]() -> bool {
+      mbar_arrive(&bars.wg_sync);
+      const bool ok = mbar_wait(&bars.wg_sync, wg_phase & 1, abort_flag);
+      ++wg_phase;
+      return __all_sync(0xffffffffu, ok);
+    };
+
+    for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+      int role, bh, q, nxt, ncs;
+      decode(item, role, bh, q);
+      tile_counts(q, nxt, ncs);
+      const size_t hb = (size_t)bh * T * D;
+      const T16* Xg = (const T16*)p.x[role] + hb;
+      // per-query vectors and scalars
+      if (!wg_sync()) { alive = false; break; }  // previous item's readers of qv / dov / red are done
+      float dq_part = 0.f;
+      if (row < D) {
+        const float qf = to_f(((const T16*)p.q)[hb + (size_t)q * D + row]);
+        const float dof = to_f(((const T16*)p.d_o)[hb + (size_t)q * D + row]);
+        qv[row] = qf;
+        dov[row] = dof;
+        dq_part = dof * to_f(((const T16*)p.o)[hb + (size_t)q * D + row]);
+      }
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) dq_part += __shfl_xor_sync(0xffffffffu, dq_part, o);
+      if (lane == 0) red[wq] = dq_part;
+      if (!wg_sync()) { alive = false; break; }
+      const float Dq = red[0] + red[1] + red[2] + red[3];
+      const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e;
+      const float scale2 = p.alpha * kLog2e;
+      float dQ_run = 0.f;  // role 0: thread `row` owns dQ[q, row]
+      if (!wg_sync()) { alive = false; break; }  // red is reused by the tile folds
+
+      for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
+        // ---- operand formation (in place): A = scale2*Q[q] (.) X tile,  A' = dO[q] (.) Y tile
+        alive = __all_sync(0xffffffffu, mbar_wait(&bars.xy_full, xt_count & 1, abort_flag));
+        if (!alive) break;
+#pragma unroll 4
+        for (int cc = 0; cc < D / 8; ++cc) {
+          const uint32_t off = (cc >> 3) * 16384 + swz128(row, cc & 7);
+          uint4 xv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA + off);
+          uint4 yv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA2 + off);
+          uint32_t wx[4] = {xv.x, xv.y, xv.z, xv.w}, wy[4] = {yv.x, yv.y, yv.z, yv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = cc * 8 + 2 * e;
+            const float2 fx = unpack2<T16>(wx[e]), fy = unpack2<T16>(wy[e]);
+            wx[e] = pack2<T16>(fx.x * (scale2 * qv[h]), fx.y * (scale2 * qv[h + 1]));
+            wy[e] = pack2<T16>(fy.x * dov[h], fy.y * dov[h + 1]);
+          }
+          *reinterpret_cast<uint4*>(smem + Cfg::kOffA + off) = make_uint4(wx[0], wx[1], wx[2], wx[3]);
+          *reinterpret_cast<uint4*>(smem + Cfg::kOffA2 + off) = make_uint4(wy[0], wy[1], wy[2], wy[3]);
+        }
+        fence_async_smem();
+        tc_fence_before();
+        mbar_arrive(&bars.a_ready);
+
+        const int x_r = xt * 128 + row;
+        const bool row_valid = p.causal ? (x_r <= q) : (x_r < T);
+
+        // ---- slabs: (S, dP) -> (P, dS)
+        for (int c = 0; c < ncs; ++c, ++n) {
+          const uint32_t b = n & 1;
+          alive = __all_sync(0xffffffffu, mbar_wait(&bars.sdp_ready[b], (n >> 1) & 1, abort_flag));
+          if (!alive) break;
+          tc_fence_after();
+          if (c == ncs - 1) {
+            // every S / dP product of this tile has completed: the operand tiles may be reloaded
+            fence_async_smem();
+            mbar_arrive(&bars.a_free);
+          }
+          const int cmax = row_valid ? (p.causal ? q : T - 1) - c * kBC : -1;
+          const uint32_t tS = tmem + lane_base + Cfg::kTmemS + b * kBC;
+          const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + b * kBC;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t s[32], dp[32];
+            tmem_ld32(tS + half * 32, s);
+            tmem_ld32(tDP + half * 32, dp);
+            tmem_wait_ld();
+            uint32_t pk[16], dk[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
+              if (half * 32 + i > cmax) p0 = 0.f;
+              if (half * 32 + i + 1 > cmax) p1 = 0.f;
+              const float d0 = p0 * (__uint_as_float(dp[i]) - Dq), d1 = p1 * (__uint_as_float(dp[i + 1]) - Dq);
+              pk[i >> 1] = pack2<T16>(p0, p1);
+              dk[i >> 1] = pack2<T16>(d0, d1);
+            }
+            tmem_st16(tS + half * 16, pk);
+            tmem_st16(tDP + half * 16, dk);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&bars.pds_ready[b]);
+        }
+        if (!alive) break;
+
+        // ---- fold G / U of this tile into the gradients
+        alive = __all_sync(0xffffffffu, mbar_wait(&bars.gu_done, xt_count & 1, abort_flag));
+        if (!alive) break;
+        tc_fence_after();
+        const bool store_row = row_valid && x_r < T;
+        float* dXr = p.dX[role] + hb + (size_t)x_r * D;
+        float* dYr = p.dY[role] + hb + (size_t)x_r * D;
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          uint32_t g[32];
+          tmem_ld32(tmem + lane_base + Cfg::kTmemG + ch * 32, g);
+          tmem_wait_ld();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = p.alpha * __uint_as_float(g[i]);
+          if (store_row) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const int h = ch * 32 + i;
+              red_add_v4(dXr + h, v[i] * qv[h], v[i + 1] * qv[h + 1], v[i + 2] * qv[h + 2], v[i + 3] * qv[h + 3]);
+            }
+          }
+          if (role == 0) {
+            // dQ[q,h] += alpha sum_r G[r,h] X[x_r,h]
+#pragma unroll
+            for (int i4 = 0; i4 < 4; ++i4) {
+              uint4 xv = make_uint4(0, 0, 0, 0);
+              if (store_row) xv = __ldg(reinterpret_cast<const uint4*>(Xg + (size_t)x_r * D + ch * 32 + i4 * 8));
+              const uint32_t wx[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack2<T16>(wx[e]);
+                v[i4 * 8 + 2 * e] *= f.x;
+                v[i4 * 8 + 2 * e + 1] *= f.y;
+              }
+            }
+            const float colsum = warp_transpose_sum(v, lane);
+            red[wq * D + ch * 32 + lane] = colsum;
+          }
+          uint32_t u[32];
+          tmem_ld32(tmem + lane_base + Cfg::kTmemU + ch * 32, u);
+          tmem_wait_ld();
+          if (store_row) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const int h = ch * 32 + i;
+              red_add_v4(dYr + h, __uint_as_float(u[i]) * dov[h], __uint_as_float(u[i + 1]) * dov[h + 1],
+                         __uint_as_float(u[i + 2]) * dov[h + 2], __uint_as_float(u[i + 3]) * dov[h + 3]);
+            }
+          }
+        }
+        if (role == 0) {
+          if (!wg_sync()) { alive = false; break; }
+          if (row < D) dQ_run += red[row] + red[D + row] + red[2 * D + row] + red[3 * D + row];
+          if (!wg_sync()) { alive = false; break; }
+        }
+        tc_fence_before();  // TMEM reads of G / U precede the next tile's first accumulate
+      }
+      if (!alive) break;
+      if (role == 0 && row < D) ((T16*)p.dq)[hb + (size_t)q * D + row] = from_f<T16>(dQ_run);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+  if (tid == 0 && bars.abort_flag && p.status) atomicOr(p.status, 4);
+}
+
+template <int D, typename T16>
+int launch_bwd(const TdpArgs& a) {
+  using Cfg = BwdCfg<D>;
+  const int BN = a.B * a.N;
+  const size_t n = (size_t)BN * a.T * a.D;
+  float* part = (float*)a.workspace;          // dK1 | dK2 | dSiLU(V1) | dV2
+  T16* sv1 = (T16*)(part + 4 * n);
+  TRITT_CUDA_OK(cudaMemsetAsync(part, 0, 4 * n * sizeof(float), a.stream));
+  silu_kernel<T16><<<(unsigned)((n / 8 + 255) / 256 + 1), 256, 0, a.stream>>>((const T16*)a.v1, sv1, n);
+  TRITT_CUDA_OK(cudaGetLastError());
+  CUtensorMap tmK1, tmK2, tmSV1, tmV2, tmK1r, tmK2r, tmSV1r, tmV2r;
+  int rc;
+  if ((rc = make_tmap_3d(&tmK1, a.k1, 2, D, a.T, BN, 64, kBC))) return rc;
+  if ((rc = make_tmap_3d(&tmK2, a.k2, 2, D, a.T, BN, 64, kBC))) return rc;
+  if ((rc = make_tmap_3d(&tmSV1, sv1, 2, D, a.T, BN, 64, kBC))) return rc;
+  if ((rc = make_tmap_3d(&tmV2, a.v2, 2, D, a.T, BN, 64, kBC))) return rc;
+  if ((rc = make_tmap_3d(&tmK1r, a.k1, 2, D, a.T, BN, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmK2r, a.k2, 2, D, a.T, BN, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmSV1r, sv1, 2, D, a.T, BN, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmV2r, a.v2, 2, D, a.T, BN, 64, 128))) return rc;
+  BwdParams p{};
+  p.q = a.q; p.o = a.o; p.d_o = a.d_o; p.lse = a.lse_in; p.dq = a.dq;
+  p.x[0] = a.k2; p.y[0] = a.v2; p.x[1] = a.k1; p.y[1] = sv1;
+  p.dX[0] = part + n;      // dK2
+  p.dY[0] = part + 3 * n;  // dV2
+  p.dX[1] = part;          // dK1
+  p.dY[1] = part + 2 * n;  // dSiLU(V1)
+  p.T = a.T; p.BN = BN; p.q_mod = a.q_mod; p.q_rem = a.q_rem;
+  p.nq = a.q_rem < a.T ? (a.T - a.q_rem + a.q_mod - 1) / a.q_mod : 0;
+  p.causal = a.mask.causal;
+  p.alpha = a.alpha;
+  p.status = a.status_word;
+  if (p.nq > 0) {
+    auto kern = tdp_bwd_kernel<D, T16>;
+    TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    const long items = (long)p.nq * BN * 2;
+    const int grid = (int)(items < num_sms() ? items : num_sms());
+    kern<<<grid, kBwdThreads, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmK1r, tmK2r, tmSV1r, tmV2r, p);
+    TRITT_CUDA_OK(cudaGetLastError());
+  }
+  if (a.flags & TRITT_FLAG_BWD_PARTIAL) return 0;
+  return simt_tdp_bwd_finalize(a.v1, a.dk1, a.dk2, a.dv1, a.dv2, n, a.dtype, part, a.stream);
+}
+
+}  // namespace
+
+size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D) {
+  const size_t n = (size_t)B * N * T * D;
+  return 4 * n * sizeof(float) + n * 2;
+}
+
+int sm100_tdp_bwd(const TdpArgs& a) {
+  if (a.dtype == TRITT_BF16) return a.D == 128 ? launch_bwd<128, __nv_bfloat16>(a) : launch_bwd<64, __nv_bfloat16>(a);
+  return a.D == 128 ? launch_bwd<128, __half>(a) : launch_bwd<64, __half>(a);
+}
+
+}  // namespace tritt

@@ -25,6 +25,7 @@
 // is uniform over the rows), and rows with k > q get weight zero in the fold.
 #include "tritt_common.cuh"
 #include "tritt_sm100.cuh"
+#include "tritt_sm100_tdp.cuh"
 
 #include <type_traits>
 
@@ -66,39 +67,6 @@ struct Barriers {
   uint32_t tmem_base;
   int abort_flag;
 };
-
-template <typename T16> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
-  __half2 v = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-template <typename T16> __device__ __forceinline__ float2 unpack2(uint32_t v);
-template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
-  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
-}
-template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
-  return __half22float2(*reinterpret_cast<__half2*>(&v));
-}
-
-// Sum of v[0..31] over the 32 lanes of a warp, column-wise: on return lane i holds the
-// total of column i.  31 shuffles instead of 32 full reductions.
-__device__ __forceinline__ float warp_transpose_sum(float (&v)[32], int lane) {
-#pragma unroll
-  for (int half = 16; half >= 1; half >>= 1) {
-    const bool upper = lane & half;
-#pragma unroll
-    for (int i = 0; i < half; ++i) {
-      const float keep = upper ? v[i + half] : v[i];
-      const float send = upper ? v[i] : v[i + half];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
-    }
-  }
-  return v[0];
-}
 
 template <int D, typename T16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -498,36 +466,6 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   if (tid == 0 && bars.abort_flag && p.status) atomicOr(p.status, 2);
 }
 
-// SiLU(V1) in the input dtype, computed once per call (the reference does the same as a
-// separate PyTorch pass, flash_trittention.py:61-62); the value tiles are then plain TMA loads.
-template <typename T16>
-__global__ void silu_kernel(const T16* __restrict__ in, T16* __restrict__ out, size_t n) {
-  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (i + 8 <= n) {
-    const uint4 v = *reinterpret_cast<const uint4*>(in + i);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t o[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f = unpack2<T16>(w[e]);
-      o[e] = pack2<T16>(silu_f(f.x), silu_f(f.y));
-    }
-    *reinterpret_cast<uint4*>(out + i) = make_uint4(o[0], o[1], o[2], o[3]);
-  } else {
-    for (; i < n; ++i) out[i] = from_f<T16>(silu_f(to_f(in[i])));
-  }
-}
-
-int num_sms() {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
-  }
-  return sms;
-}
-
 template <int D, typename T16>
 int launch_fwd(const TdpArgs& a) {
   using Cfg = FwdCfg<D>;
@@ -568,7 +506,7 @@ int launch_fwd(const TdpArgs& a) {
 }  // namespace
 
 bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m) {
-  if (op != TRITT_OP_TDP_FWD) return false;
+  if (op != TRITT_OP_TDP_FWD && op != TRITT_OP_TDP_BWD) return false;
   if (dtype != TRITT_BF16 && dtype != TRITT_F16) return false;
   if (D != 64 && D != 128) return false;
   if (!m.full_windows()) return false;
@@ -578,6 +516,7 @@ bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m) {
 size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype) {
   if (dtype != TRITT_BF16 && dtype != TRITT_F16) return 0;
   if (op == TRITT_OP_TDP_FWD) return (size_t)B * N * T * D * 2;
+  if (op == TRITT_OP_TDP_BWD) return sm100_tdp_bwd_workspace(B, N, T, D);
   return 0;
 }
 
@@ -589,11 +528,6 @@ int sm100_tdp_fwd(const TdpArgs& a) {
   }
   if (a.dtype == TRITT_BF16) return a.D == 128 ? launch_fwd<128, __nv_bfloat16>(a) : launch_fwd<64, __nv_bfloat16>(a);
   return a.D == 128 ? launch_fwd<128, __half>(a) : launch_fwd<64, __half>(a);
-}
-
-int sm100_tdp_bwd(const TdpArgs&) {
-  set_error("tensor-core backward is not available");
-  return -100;
 }
 
 }  // namespace tritt

@@ -83,3 +83,71 @@ def test_autograd_entry_point_uses_tensor_core_forward():
     assert float((out.float().cpu() - z_ref).abs().max()) <= 2e-2
     for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, g_ref):
         assert float((leaf.grad.float().cpu() - ref).abs().max()) <= 2e-2 * max(1.0, float(ref.abs().max())), name
+
+
+def _bwd_case(B, N, T, D, dtype, causal, scale_in, alpha, seed):
+    q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, scale=scale_in, seed=seed, dtype=dtype)
+    code = _native.dtype_code(dtype)
+    assert _native.tdp_path(_native.OP_TDP_BWD, T, D, code, causal, None, None, None, None) == _native.PATH_TCGEN05
+    leaves = [x.to(DEV).requires_grad_(True) for x in (q, k1, k2, v1, v2)]
+    out = flash_trittention(*leaves, alpha, None, None, None, None, causal)
+    out.backward(dz.to(DEV))
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0, "a bounded barrier wait ran out"
+    f = [x.float() for x in (q, k1, k2, v1, v2)]
+    g_ref = orc.tdp_backward(*f, dz.float(), alpha, causal)
+    errs = {}
+    for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, g_ref):
+        errs[name] = (float((leaf.grad.float().cpu() - ref).abs().max()), float(ref.abs().max()))
+    return errs
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("T", [40, 64, 100, 129, 256])
+@pytest.mark.parametrize("causal", [True, False])
+def test_backward_bf16_matches_oracle(T, D, causal):
+    errs = _bwd_case(1, 2, T, D, torch.bfloat16, causal, 0.5, 1.0 / D, seed=2 * T + D)
+    for name, (err, mag) in errs.items():
+        assert err <= TOL[torch.bfloat16] * max(1.0, mag), (name, err, mag)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_backward_fp16_matches_oracle(D):
+    errs = _bwd_case(2, 2, 200, D, torch.float16, True, 0.5, 1.0 / D, seed=4)
+    for name, (err, mag) in errs.items():
+        assert err <= TOL[torch.float16] * max(1.0, mag), (name, err, mag)
+
+
+def test_backward_unit_variance_inputs():
+    errs = _bwd_case(1, 2, 160, 64, torch.float16, True, 1.0, 1 / 8, seed=19)
+    for name, (err, mag) in errs.items():
+        assert err <= 2e-2 * max(1.0, mag), (name, err, mag)
+
+
+def test_backward_query_shards_sum_to_full_gradient():
+    """Query-sharded backward: each shard writes its rows of dq and leaves fp32 partial key-side sums;
+    their sum, finalised once, equals the unsharded gradients (the multi-device path does the sum with
+    an all-reduce)."""
+    B, N, T, D, alpha = 1, 2, 200, 64, 1 / 64
+    q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, scale=0.5, seed=23, dtype=torch.bfloat16)
+    t = [x.to(DEV) for x in (q, k1, k2, v1, v2)]
+    do = dz.to(DEV)
+    o, lse = torch.empty_like(t[0]), torch.empty(B, N, T, device=DEV)
+    _native.tdp_fwd(*t, o, lse, alpha, True, None, None, None, None)
+    full = [torch.empty_like(t[0]) for _ in range(5)]
+    _native.tdp_bwd(*t, o, do, lse, *full, alpha, True, None, None, None, None)
+    dq = torch.zeros_like(t[0])
+    n = t[0].numel()
+    acc = torch.zeros(4 * n, device=DEV)
+    for rem in range(4):
+        ws = _native.tdp_bwd(*t, o, do, lse, dq, None, None, None, None, alpha, True, None, None, None, None,
+                             q_mod=4, q_rem=rem, flags=_native.FLAG_BWD_PARTIAL)
+        acc += ws[: 16 * n].view(torch.float32)
+    ws = _native.workspace(_native.OP_TDP_BWD, B, N, T, D, _native.BF16, DEV)
+    ws[: 16 * n].view(torch.float32).copy_(acc)
+    outs = [torch.empty_like(t[0]) for _ in range(4)]
+    _native.tdp_bwd_finalize(t[3], *outs, ws)
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0
+    for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), [dq] + outs, full):
+        assert float((a.float() - b.float()).abs().max()) <= 2e-2 * max(1.0, float(b.float().abs().max())), name
