@@ -2,6 +2,7 @@
 // the tensor-core (tcgen05) kernels and the general CUDA-core kernels.
 #include "tritt_common.cuh"
 
+#include <atomic>
 #include <cstring>
 
 namespace tritt {
@@ -15,6 +16,10 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 const char* get_error() { return g_err; }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+unsigned long long launches() { return g_launches.load(std::memory_order_relaxed); }
 
 namespace {
 
@@ -80,6 +85,8 @@ using namespace tritt;
 extern "C" {
 
 int tritt_version(void) { return 100; }
+
+unsigned long long tritt_kernel_launches(void) { return tritt::launches(); }
 
 const char* tritt_last_error(void) { return get_error(); }
 

@@ -19,7 +19,9 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 // ---------------------------------------------------------------- error reporting
 void set_error(const char* fmt, ...);
+void count_launch();  // bumps the process-wide count of kernels this library has enqueued
 const char* get_error();
+unsigned long long launches();
 
 #define TRITT_CUDA_OK(expr)                                                              \
   do {                                                                                   \

@@ -311,6 +311,7 @@ int launch_attn(K kern, const AttnParams& p, int nvec, int ntiles, int BN, cudaS
   }
   TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
   kern<<<dim3((p.T + nt - 1) / nt, BN), nt, sm, stream>>>(p);
+  count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -373,6 +374,7 @@ int dps_bwd_t(const DpsArgs& a) {
   int rc = dps_inner_fwd<T>(a, w);
   if (rc) return rc;
   rowdot_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
+  count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   // ---- outer attention: rows q (Q), columns t (K2, W = Y*V2, bias LSEin)
   AttnParams p{};
@@ -396,6 +398,7 @@ int dps_bwd_t(const DpsArgs& a) {
   if (rc) return rc;
   dps_mid_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>(w.dW, w.Y, (const T*)a.v2, w.g, (T*)a.dv2, w.dY,
                                                                         w.Dt, r, a.D);
+  count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   // ---- inner attention: rows t (K2), columns s (K1, SiLU(V1)); upstream gradient dY
   AttnParams q{};
@@ -418,6 +421,7 @@ int dps_bwd_t(const DpsArgs& a) {
   rc = launch_attn(attn_bwd_col_kernel<T>, qc, 4, 3, BN, a.stream);
   if (rc) return rc;
   dps_dv1_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, a.stream>>>(w.dsV1, (const T*)a.v1, (T*)a.dv1, n);
+  count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -252,6 +252,7 @@ int launch(const SimtTdpParams& p, int BN, cudaStream_t stream) {
   TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
   if (p.nq <= 0) return 0;
   kern<<<dim3(p.nq, BN), nt, sm, stream>>>(p);
+  count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -304,12 +305,15 @@ int simt_tdp_bwd_finalize(const void* v1, void* dk1, void* dk2, void* dv1, void*
   switch (dtype) {
     case TRITT_F32:
       tdp_finalize_kernel<float><<<nb, nt, 0, stream>>>((const float*)v1, (float*)dk1, (float*)dk2, (float*)dv1, (float*)dv2, part, n);
+      count_launch();
       break;
     case TRITT_F16:
       tdp_finalize_kernel<__half><<<nb, nt, 0, stream>>>((const __half*)v1, (__half*)dk1, (__half*)dk2, (__half*)dv1, (__half*)dv2, part, n);
+      count_launch();
       break;
     case TRITT_BF16:
       tdp_finalize_kernel<__nv_bfloat16><<<nb, nt, 0, stream>>>((const __nv_bfloat16*)v1, (__nv_bfloat16*)dk1, (__nv_bfloat16*)dk2, (__nv_bfloat16*)dv1, (__nv_bfloat16*)dv2, part, n);
+      count_launch();
       break;
     default:
       set_error("unknown dtype %d", dtype);

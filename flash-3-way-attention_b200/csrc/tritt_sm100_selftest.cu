@@ -169,9 +169,11 @@ extern "C" int tritt_selftest_umma(const void* A, const void* Bm, const void* V,
   if (dtype == TRITT_BF16) {
     TRITT_CUDA_OK(cudaFuncSetAttribute(umma_selftest_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     umma_selftest_kernel<true><<<1, 128, smem, (cudaStream_t)stream>>>(tmA, tmB, tmV, C, C2, status_word);
+    count_launch();
   } else {
     TRITT_CUDA_OK(cudaFuncSetAttribute(umma_selftest_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     umma_selftest_kernel<false><<<1, 128, smem, (cudaStream_t)stream>>>(tmA, tmB, tmV, C, C2, status_word);
+    count_launch();
   }
   TRITT_CUDA_OK(cudaGetLastError());
   return 0;

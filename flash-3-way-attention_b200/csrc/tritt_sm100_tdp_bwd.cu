@@ -24,13 +24,16 @@
 // tiles x <= q and, inside, the column slabs c <= q.
 #include "tritt_sm100_tdp.cuh"
 
+#include <cstdlib>
 #include <type_traits>
 
 namespace tritt {
+#ifdef TRITT_TIMING
+__device__ long long g_timing[148 * 16];
+#endif
 namespace {
 using namespace sm100;
 
-constexpr int kBwdThreads = 256;
 constexpr int kBC = 64;  // key columns per slab
 
 template <int D> struct BwdCfg {
@@ -65,13 +68,25 @@ struct BwdBarriers {
   int abort_flag;
 };
 
+#ifdef TRITT_TIMING
+// Development build only: per-CTA cycle counters of where each role waits.
+
+#define TT_DECL long long tt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tt_t = clock64();
+#define TT(slot) { const long long tt_n = clock64(); tt_acc[slot] += tt_n - tt_t; tt_t = tt_n; }
+#define TT_FLUSH(basei) if (blockIdx.x < 148) { for (int i = 0; i < 8; ++i) g_timing[blockIdx.x * 16 + (basei) + i] = tt_acc[i]; }
+#else
+#define TT_DECL
+#define TT(slot)
+#define TT_FLUSH(basei)
+#endif
+
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
 
-template <int D, typename T16>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+template <int D, typename T16, int NWG>
+__global__ void __launch_bounds__(128 + 128 * NWG, 1)
 tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__ CUtensorMap tmK2,
                const __grid_constant__ CUtensorMap tmSV1, const __grid_constant__ CUtensorMap tmV2,
                const __grid_constant__ CUtensorMap tmK1r, const __grid_constant__ CUtensorMap tmK2r,
@@ -91,14 +106,14 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       mbar_init(&bars.ring_empty[i], 1);
     }
     mbar_init(&bars.xy_full, 1);
-    mbar_init(&bars.a_ready, 128);
-    mbar_init(&bars.a_free, 128);
+    mbar_init(&bars.a_ready, 128 * NWG);
+    mbar_init(&bars.a_free, 128 * NWG);
     mbar_init(&bars.gu_done, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.sdp_ready[b], 1);
-      mbar_init(&bars.pds_ready[b], 128);
+      mbar_init(&bars.pds_ready[b], 128 * NWG);
     }
-    mbar_init(&bars.wg_sync, 128);
+    mbar_init(&bars.wg_sync, 128 * NWG);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -136,10 +151,15 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       auto load_stage = [&](const CUtensorMap* tm, int row0, int bh) -> bool {
         const int st = pos % NS;
         if (!mbar_wait(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag)) return false;
+#ifdef TRITT_EXP_NOTMA
+        mbar_arrive(&bars.ring_full[st]);
+        (void)tm; (void)row0; (void)bh;
+#else
         mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kStage);
         for (int hh = 0; hh < KH; ++hh)
           tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kStage + hh * (kBC * 128), tm, &bars.ring_full[st], hh * 64,
                       row0, bh);
+#endif
         ++pos;
         return true;
       };
@@ -180,53 +200,70 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       constexpr int kFmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = make_idesc_f16(128, kBC, kFmt, false, false);
       constexpr uint32_t idesc_g = make_idesc_f16(128, D, kFmt, false, true);
-      const uint32_t sA = smem_u32(smem + Cfg::kOffA), sA2 = smem_u32(smem + Cfg::kOffA2);
-      const uint32_t sRing = smem_u32(smem + Cfg::kOffRing);
+      // descriptor low words; per instruction only a constant (in 16-byte units) is added
+      constexpr uint32_t kHi = desc_hi(1024);
+      constexpr uint32_t kStage16 = Cfg::kStage >> 4;
+      const uint32_t aLo = desc_lo(smem_u32(smem + Cfg::kOffA), 16), a2Lo = desc_lo(smem_u32(smem + Cfg::kOffA2), 16);
+      const uint32_t ringK = desc_lo(smem_u32(smem + Cfg::kOffRing), 16);           // K-major view of a stage
+      const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), kBC * 128);   // row-major (MN-major) view
       uint32_t xt_count = 0, base = 0, n = 0;
       bool alive = true;
-      auto wait_full = [&](uint32_t pos) { return mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag); };
+      TT_DECL
+      auto wait_full = [&](uint32_t pos) {
+        TT(0)
+        const bool ok = mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
+        TT(1)
+        return ok;
+      };
       // S(slab) = A Kc^T and dP(slab) = A' Vc^T
       auto issue_sdp = [&](uint32_t slab_n, uint32_t pos) -> bool {
         const uint32_t b = slab_n & 1;
         if (!wait_full(pos)) return false;
         {
-          const uint32_t st = pos % NS;
+          const uint32_t bLo = ringK + (pos % NS) * kStage16;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
-            const uint64_t da = make_smem_desc(sA + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-            const uint64_t db = make_smem_desc(sRing + st * Cfg::kStage + (k >> 2) * (kBC * 128) + (k & 3) * 32, 16, 1024);
-            mma_ss(tmem + Cfg::kTmemS + b * kBC, da, db, idesc_s, k > 0);
+            const uint32_t ka = (k >> 2) * (16384 >> 4) + (k & 3) * 2, kb = (k >> 2) * ((kBC * 128) >> 4) + (k & 3) * 2;
+            mma_ss_lo(tmem + Cfg::kTmemS + b * kBC, aLo + ka, bLo + kb, kHi, idesc_s, k > 0);
           }
+          TT(4)
         }
         if (!wait_full(pos + 1)) return false;
         {
-          const uint32_t st = (pos + 1) % NS;
+          const uint32_t bLo = ringK + ((pos + 1) % NS) * kStage16;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
-            const uint64_t da = make_smem_desc(sA2 + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-            const uint64_t db = make_smem_desc(sRing + st * Cfg::kStage + (k >> 2) * (kBC * 128) + (k & 3) * 32, 16, 1024);
-            mma_ss(tmem + Cfg::kTmemDP + b * kBC, da, db, idesc_s, k > 0);
+            const uint32_t ka = (k >> 2) * (16384 >> 4) + (k & 3) * 2, kb = (k >> 2) * ((kBC * 128) >> 4) + (k & 3) * 2;
+            mma_ss_lo(tmem + Cfg::kTmemDP + b * kBC, a2Lo + ka, bLo + kb, kHi, idesc_s, k > 0);
           }
+          TT(5)
         }
         mma_commit(&bars.sdp_ready[b]);
+        TT(7)
         return true;
       };
       // G (+)= dS Kc and U (+)= P Vc, then hand the two ring stages back
       auto issue_gu = [&](uint32_t slab_n, uint32_t pos, bool accumulate) {
         const uint32_t b = slab_n & 1;
         const uint32_t stK = pos % NS, stV = (pos + 1) % NS;
+        // Each warpgroup packed its columns of P and dS into its own column range of the S slab:
+        // P in the first half of the range, dS in the second half.
+        constexpr int CW = kBC / NWG, KPW = CW / 16;  // columns, and 16-deep MMA steps, per warpgroup
+        const uint32_t acc = accumulate ? 1u : 0u;
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
-          const uint64_t db = make_smem_desc(sRing + stK * Cfg::kStage + k * 2048, kBC * 128, 1024);
-          mma_ts(tmem + Cfg::kTmemG, tmem + Cfg::kTmemDP + b * kBC + k * 8, db, idesc_g, accumulate || k > 0);
+          const uint32_t a = tmem + Cfg::kTmemS + b * kBC + (k / KPW) * CW + CW / 2 + (k % KPW) * 8;
+          mma_ts_lo(tmem + Cfg::kTmemG, a, ringMN + stK * kStage16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
         }
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
-          const uint64_t db = make_smem_desc(sRing + stV * Cfg::kStage + k * 2048, kBC * 128, 1024);
-          mma_ts(tmem + Cfg::kTmemU, tmem + Cfg::kTmemS + b * kBC + k * 8, db, idesc_g, accumulate || k > 0);
+          const uint32_t a = tmem + Cfg::kTmemS + b * kBC + (k / KPW) * CW + (k % KPW) * 8;
+          mma_ts_lo(tmem + Cfg::kTmemU, a, ringMN + stV * kStage16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
         }
+        TT(6)
         mma_commit(&bars.ring_empty[stK]);
         mma_commit(&bars.ring_empty[stV]);
+        TT(7)
       };
 
       for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
@@ -234,14 +271,18 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         decode(item, role, bh, q);
         tile_counts(q, nxt, ncs);
         for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
+          TT(0)
           if (!mbar_wait(&bars.a_ready, xt_count & 1, abort_flag)) { alive = false; break; }
+          TT(2)
           tc_fence_after();
           const uint32_t n0 = n;
           if (!issue_sdp(n0, base)) { alive = false; break; }
           if (ncs > 1 && !issue_sdp(n0 + 1, base + 2)) { alive = false; break; }
           for (int c = 0; c < ncs && alive; ++c) {
             const uint32_t sn = n0 + c;
+            TT(0)
             if (!mbar_wait(&bars.pds_ready[sn & 1], (sn >> 1) & 1, abort_flag)) { alive = false; break; }
+            TT(3)
             tc_fence_after();
             issue_gu(sn, base + 2 * c, c > 0);
             if (c + 2 < ncs) {
@@ -253,9 +294,16 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           base += 2 * ncs;
         }
       }
+      TT(0)
+      TT_FLUSH(0)
     }
   } else if (warp >= 4) {
-    // ------------------------------------------------------------------ soft-max / gradient warpgroup
+    // ------------------------------------------------------------------ soft-max / gradient warpgroups
+    // NWG warpgroups share every tile: warpgroup g owns the columns [g*CW, (g+1)*CW) of each slab and
+    // the head-dimension range [g*HW, (g+1)*HW) of the operand formation and of the gradient fold.
+    constexpr int CW = kBC / NWG;   // slab columns per warpgroup
+    constexpr int HW = D / NWG;     // head-dimension columns per warpgroup
+    const int wg = (warp - 4) >> 2;
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
@@ -264,6 +312,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     float* dov = qv + D;                        // dO[q, :]
     uint32_t xt_count = 0, n = 0, wg_phase = 0;
     bool alive = true;
+    TT_DECL
     auto wg_sync = [&]() -> bool {
       mbar_arrive(&bars.wg_sync);
       const bool ok = mbar_wait(&bars.wg_sync, wg_phase & 1, abort_flag);
@@ -279,30 +328,35 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       const T16* Xg = (const T16*)p.x[role] + hb;
       // per-query vectors and scalars
       if (!wg_sync()) { alive = false; break; }  // previous item's readers of qv / dov / red are done
-      float dq_part = 0.f;
-      if (row < D) {
-        const float qf = to_f(((const T16*)p.q)[hb + (size_t)q * D + row]);
-        const float dof = to_f(((const T16*)p.d_o)[hb + (size_t)q * D + row]);
-        qv[row] = qf;
-        dov[row] = dof;
-        dq_part = dof * to_f(((const T16*)p.o)[hb + (size_t)q * D + row]);
-      }
+      if (wg == 0) {
+        float dq_part = 0.f;
+        if (row < D) {
+          const float qf = to_f(((const T16*)p.q)[hb + (size_t)q * D + row]);
+          const float dof = to_f(((const T16*)p.d_o)[hb + (size_t)q * D + row]);
+          qv[row] = qf;
+          dov[row] = dof;
+          dq_part = dof * to_f(((const T16*)p.o)[hb + (size_t)q * D + row]);
+        }
 #pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) dq_part += __shfl_xor_sync(0xffffffffu, dq_part, o);
-      if (lane == 0) red[wq] = dq_part;
+        for (int o = 16; o >= 1; o >>= 1) dq_part += __shfl_xor_sync(0xffffffffu, dq_part, o);
+        if (lane == 0) red[wq] = dq_part;
+      }
       if (!wg_sync()) { alive = false; break; }
       const float Dq = red[0] + red[1] + red[2] + red[3];
       const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e;
       const float scale2 = p.alpha * kLog2e;
-      float dQ_run = 0.f;  // role 0: thread `row` owns dQ[q, row]
+      float dQ_run = 0.f;  // role 0: thread `row` of warpgroup 0 owns dQ[q, row]
       if (!wg_sync()) { alive = false; break; }  // red is reused by the tile folds
 
       for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
         // ---- operand formation (in place): A = scale2*Q[q] (.) X tile,  A' = dO[q] (.) Y tile
+        TT(0)
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.xy_full, xt_count & 1, abort_flag));
+        TT(1)
         if (!alive) break;
-#pragma unroll 4
-        for (int cc = 0; cc < D / 8; ++cc) {
+#pragma unroll
+        for (int ci = 0; ci < HW / 8; ++ci) {
+          const int cc = wg * (HW / 8) + ci;
           const uint32_t off = (cc >> 3) * 16384 + swz128(row, cc & 7);
           uint4 xv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA + off);
           uint4 yv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA2 + off);
@@ -324,10 +378,12 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         const int x_r = xt * 128 + row;
         const bool row_valid = p.causal ? (x_r <= q) : (x_r < T);
 
-        // ---- slabs: (S, dP) -> (P, dS)
+        // ---- slabs: (S, dP) -> (P, dS), this warpgroup's CW columns
         for (int c = 0; c < ncs; ++c, ++n) {
           const uint32_t b = n & 1;
+          TT(2)
           alive = __all_sync(0xffffffffu, mbar_wait(&bars.sdp_ready[b], (n >> 1) & 1, abort_flag));
+          TT(3)
           if (!alive) break;
           tc_fence_after();
           if (c == ncs - 1) {
@@ -335,43 +391,58 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             fence_async_smem();
             mbar_arrive(&bars.a_free);
           }
-          const int cmax = row_valid ? (p.causal ? q : T - 1) - c * kBC : -1;
-          const uint32_t tS = tmem + lane_base + Cfg::kTmemS + b * kBC;
-          const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + b * kBC;
+          const int cmax = (row_valid ? (p.causal ? q : T - 1) - c * kBC : -1) - wg * CW;
+          const uint32_t tS = tmem + lane_base + Cfg::kTmemS + b * kBC + wg * CW;
+          const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + b * kBC + wg * CW;
+#ifndef TRITT_EXP_NOSOFTMAX
+          uint32_t s[CW], dp[CW];
+          tmem_ld(tS, s);
+          tmem_ld(tDP, dp);
+          tmem_wait_ld();
+          uint32_t pk[CW / 2], dk[CW / 2];
+          if (cmax >= CW - 1) {
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t s[32], dp[32];
-            tmem_ld32(tS + half * 32, s);
-            tmem_ld32(tDP + half * 32, dp);
-            tmem_wait_ld();
-            uint32_t pk[16], dk[16];
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
-              if (half * 32 + i > cmax) p0 = 0.f;
-              if (half * 32 + i + 1 > cmax) p1 = 0.f;
+            for (int i = 0; i < CW; i += 2) {
+              const float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
               const float d0 = p0 * (__uint_as_float(dp[i]) - Dq), d1 = p1 * (__uint_as_float(dp[i + 1]) - Dq);
               pk[i >> 1] = pack2<T16>(p0, p1);
               dk[i >> 1] = pack2<T16>(d0, d1);
             }
-            tmem_st16(tS + half * 16, pk);
-            tmem_st16(tDP + half * 16, dk);
+          } else {
+#pragma unroll
+            for (int i = 0; i < CW; i += 2) {
+              float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
+              if (i > cmax) p0 = 0.f;
+              if (i + 1 > cmax) p1 = 0.f;
+              const float d0 = p0 * (__uint_as_float(dp[i]) - Dq), d1 = p1 * (__uint_as_float(dp[i + 1]) - Dq);
+              pk[i >> 1] = pack2<T16>(p0, p1);
+              dk[i >> 1] = pack2<T16>(d0, d1);
+            }
           }
+          tmem_st(tS, pk);            // P  -> first half of this warpgroup's column range
+          tmem_st(tS + CW / 2, dk);   // dS -> second half
           tmem_wait_st();
+#else
+          (void)cmax; (void)tS; (void)tDP; (void)lse2; (void)Dq;
+#endif
           tc_fence_before();
           mbar_arrive(&bars.pds_ready[b]);
         }
         if (!alive) break;
 
-        // ---- fold G / U of this tile into the gradients
+        // ---- fold G / U of this tile into the gradients (32-column chunks dealt round-robin to the warpgroups)
+        TT(2)
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.gu_done, xt_count & 1, abort_flag));
+        TT(4)
         if (!alive) break;
         tc_fence_after();
         const bool store_row = row_valid && x_r < T;
         float* dXr = p.dX[role] + hb + (size_t)x_r * D;
         float* dYr = p.dY[role] + hb + (size_t)x_r * D;
 #pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
+        for (int ci = 0; ci < (D / 32 + NWG - 1) / NWG; ++ci) {
+          const int ch = wg + ci * NWG;  // 32-column chunk of the head dimension
+          if (ch >= D / 32) break;
           uint32_t g[32];
           tmem_ld32(tmem + lane_base + Cfg::kTmemG + ch * 32, g);
           tmem_wait_ld();
@@ -416,14 +487,16 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         }
         if (role == 0) {
           if (!wg_sync()) { alive = false; break; }
-          if (row < D) dQ_run += red[row] + red[D + row] + red[2 * D + row] + red[3 * D + row];
+          if (wg == 0 && row < D) dQ_run += red[row] + red[D + row] + red[2 * D + row] + red[3 * D + row];
           if (!wg_sync()) { alive = false; break; }
         }
         tc_fence_before();  // TMEM reads of G / U precede the next tile's first accumulate
+        TT(5)
       }
       if (!alive) break;
-      if (role == 0 && row < D) ((T16*)p.dq)[hb + (size_t)q * D + row] = from_f<T16>(dQ_run);
+      if (role == 0 && wg == 0 && row < D) ((T16*)p.dq)[hb + (size_t)q * D + row] = from_f<T16>(dQ_run);
     }
+    if (wg == 0 && row == 0) { TT_FLUSH(8) }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -433,7 +506,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   if (tid == 0 && bars.abort_flag && p.status) atomicOr(p.status, 4);
 }
 
-template <int D, typename T16>
+template <int D, typename T16, int NWG>
 int launch_bwd(const TdpArgs& a) {
   using Cfg = BwdCfg<D>;
   const int BN = a.B * a.N;
@@ -442,6 +515,7 @@ int launch_bwd(const TdpArgs& a) {
   T16* sv1 = (T16*)(part + 4 * n);
   TRITT_CUDA_OK(cudaMemsetAsync(part, 0, 4 * n * sizeof(float), a.stream));
   silu_kernel<T16><<<(unsigned)((n / 8 + 255) / 256 + 1), 256, 0, a.stream>>>((const T16*)a.v1, sv1, n);
+  count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   CUtensorMap tmK1, tmK2, tmSV1, tmV2, tmK1r, tmK2r, tmSV1r, tmV2r;
   int rc;
@@ -466,11 +540,12 @@ int launch_bwd(const TdpArgs& a) {
   p.alpha = a.alpha;
   p.status = a.status_word;
   if (p.nq > 0) {
-    auto kern = tdp_bwd_kernel<D, T16>;
+    auto kern = tdp_bwd_kernel<D, T16, NWG>;
     TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     const long items = (long)p.nq * BN * 2;
     const int grid = (int)(items < num_sms() ? items : num_sms());
-    kern<<<grid, kBwdThreads, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmK1r, tmK2r, tmSV1r, tmV2r, p);
+    kern<<<grid, 128 + 128 * NWG, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmK1r, tmK2r, tmSV1r, tmV2r, p);
+    count_launch();
     TRITT_CUDA_OK(cudaGetLastError());
   }
   if (a.flags & TRITT_FLAG_BWD_PARTIAL) return 0;
@@ -479,14 +554,38 @@ int launch_bwd(const TdpArgs& a) {
 
 }  // namespace
 
+#ifdef TRITT_TIMING
+}  // namespace tritt
+extern "C" int tritt_debug_read_timing(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, tritt::g_timing, sizeof(long long) * 148 * 16);
+}
+namespace tritt {
+#endif
+
 size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D) {
   const size_t n = (size_t)B * N * T * D;
   return 4 * n * sizeof(float) + n * 2;
 }
 
+// Number of soft-max warpgroups per CTA (2 or 4); TRITT_BWD_WG overrides the default for tuning.
+static int bwd_warpgroups() {
+  static int v = 0;
+  if (!v) {
+    const char* e = getenv("TRITT_BWD_WG");
+    v = (e && atoi(e) == 2) ? 2 : 4;
+  }
+  return v;
+}
+
+template <int D, typename T16>
+static int launch_bwd_wg(const TdpArgs& a) {
+  return bwd_warpgroups() == 2 ? launch_bwd<D, T16, 2>(a) : launch_bwd<D, T16, 4>(a);
+}
+
 int sm100_tdp_bwd(const TdpArgs& a) {
-  if (a.dtype == TRITT_BF16) return a.D == 128 ? launch_bwd<128, __nv_bfloat16>(a) : launch_bwd<64, __nv_bfloat16>(a);
-  return a.D == 128 ? launch_bwd<128, __half>(a) : launch_bwd<64, __half>(a);
+  if (a.dtype == TRITT_BF16)
+    return a.D == 128 ? launch_bwd_wg<128, __nv_bfloat16>(a) : launch_bwd_wg<64, __nv_bfloat16>(a);
+  return a.D == 128 ? launch_bwd_wg<128, __half>(a) : launch_bwd_wg<64, __half>(a);
 }
 
 }  // namespace tritt

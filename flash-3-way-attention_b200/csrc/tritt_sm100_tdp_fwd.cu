@@ -181,32 +181,33 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       constexpr int kFmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = make_idesc_f16(128, kBJ, kFmt, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, D, kFmt, false, true);
-      const uint32_t sA[2] = {smem_u32(smem + Cfg::kOffAa), smem_u32(smem + Cfg::kOffAb)};
-      const uint32_t sRing = smem_u32(smem + Cfg::kOffRing);
+      // descriptor low words; per instruction only a constant (in 16-byte units) is added
+      constexpr uint32_t kHi = desc_hi(1024);
+      constexpr uint32_t kStage16 = Cfg::kStage >> 4;
+      const uint32_t aLo[2] = {desc_lo(smem_u32(smem + Cfg::kOffAa), 16), desc_lo(smem_u32(smem + Cfg::kOffAb), 16)};
+      const uint32_t ringK = desc_lo(smem_u32(smem + Cfg::kOffRing), 16);          // K-major view of a stage
+      const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), kBJ * 128);  // row-major (MN-major) view
       uint32_t kt_count = 0, base = 0, n = 0;  // n: score slabs issued per tile so far
       bool alive = true;
       // S_x(slab) = A_x * K1tile^T
       auto issue_s = [&](int x, uint32_t slab_n, uint32_t pos) {
-        const uint32_t st = pos % NS;
+        const uint32_t bLo = ringK + (pos % NS) * kStage16;
         const uint32_t d = tmem + (x * 2 + (slab_n & 1)) * kBJ;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint64_t da = make_smem_desc(sA[x] + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc(sRing + st * Cfg::kStage + (k >> 2) * (kBJ * 128) + (k & 3) * 32, 16, 1024);
-          mma_ss(d, da, db, idesc_s, k > 0);
+          const uint32_t ka = (k >> 2) * (16384 >> 4) + (k & 3) * 2, kb = (k >> 2) * ((kBJ * 128) >> 4) + (k & 3) * 2;
+          mma_ss_lo(d, aLo[x] + ka, bLo + kb, kHi, idesc_s, k > 0);
         }
         mma_commit(&bars.s_ready[x][slab_n & 1]);
       };
       // acc_x (+)= P_x(slab) * SiLU(V1)tile
       auto issue_pv = [&](int x, uint32_t slab_n, uint32_t pos, bool accumulate) {
-        const uint32_t st = pos % NS;
+        const uint32_t bLo = ringMN + (pos % NS) * kStage16;
         const uint32_t a = tmem + (x * 2 + (slab_n & 1)) * kBJ;
         const uint32_t d = tmem + Cfg::kTmemO + x * D;
+        const uint32_t acc = accumulate ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < kBJ / 16; ++k) {
-          const uint64_t db = make_smem_desc(sRing + st * Cfg::kStage + k * 2048, kBJ * 128, 1024);
-          mma_ts(d, a + k * 8, db, idesc_pv, accumulate || k > 0);
-        }
+        for (int k = 0; k < kBJ / 16; ++k) mma_ts_lo(d, a + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv, k > 0 ? 1u : acc);
         mma_commit(&bars.pv_done[x]);
       };
       auto wait_full = [&](uint32_t pos) { return mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag); };
@@ -473,6 +474,7 @@ int launch_fwd(const TdpArgs& a) {
   const size_t n = (size_t)BN * a.T * a.D;
   T16* sv1 = (T16*)a.workspace;
   silu_kernel<T16><<<(unsigned)((n / 8 + 255) / 256 + 1), 256, 0, a.stream>>>((const T16*)a.v1, sv1, n);
+  count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   CUtensorMap tmK1, tmK2, tmSV1, tmV2;
   int rc;
@@ -499,6 +501,7 @@ int launch_fwd(const TdpArgs& a) {
   const long items = (long)p.n_pairs * BN;
   const int grid = (int)(items < num_sms() ? items : num_sms());
   kern<<<grid, kThreads, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, p);
+  count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   return 0;
 }

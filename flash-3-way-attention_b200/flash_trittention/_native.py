@@ -12,7 +12,7 @@ import threading
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtritt_sm100.so")
+LIB_PATH = os.path.join(_HERE, os.environ.get("TRITT_LIB", "libtritt_sm100.so"))
 
 F32, F16, BF16 = 0, 1, 2
 OP_TDP_FWD, OP_TDP_BWD, OP_DPS_FWD, OP_DPS_BWD = 0, 1, 2, 3
@@ -23,7 +23,7 @@ _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 # every symbol include/tritt.h declares
 SYMBOLS = (
-    "tritt_version", "tritt_last_error", "tritt_workspace_bytes", "tritt_tdp_path", "tritt_tdp_fwd",
+    "tritt_version", "tritt_kernel_launches", "tritt_last_error", "tritt_workspace_bytes", "tritt_tdp_path", "tritt_tdp_fwd",
     "tritt_tdp_bwd", "tritt_tdp_bwd_finalize", "tritt_tdp_bwd_partials_offset", "tritt_dps_fwd",
     "tritt_dps_bwd", "tritt_selftest_umma",
 )
@@ -51,6 +51,7 @@ def lib():
                 L = C.CDLL(LIB_PATH)
                 vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
                 L.tritt_version.restype = i
+                L.tritt_kernel_launches.restype = C.c_ulonglong
                 L.tritt_last_error.restype = C.c_char_p
                 L.tritt_workspace_bytes.restype = sz
                 L.tritt_workspace_bytes.argtypes = [i] * 6

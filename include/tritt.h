@@ -49,6 +49,8 @@ enum {
 enum { TRITT_PATH_SIMT = 0, TRITT_PATH_TCGEN05 = 1 };
 
 int tritt_version(void);
+/* Number of kernels this library has enqueued in the calling process so far (bookkeeping for benchmarks). */
+unsigned long long tritt_kernel_launches(void);
 const char* tritt_last_error(void);
 
 /* Bytes of caller-provided scratch the given operation needs (0 if none). */
