@@ -25,7 +25,7 @@ _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 SYMBOLS = (
     "tritt_version", "tritt_kernel_launches", "tritt_last_error", "tritt_workspace_bytes", "tritt_tdp_path", "tritt_tdp_fwd",
     "tritt_tdp_bwd", "tritt_tdp_bwd_finalize", "tritt_tdp_bwd_partials_offset", "tritt_dps_fwd",
-    "tritt_dps_bwd", "tritt_selftest_umma",
+    "tritt_dps_bwd", "tritt_selftest_umma", "tritt_tdp_fwd_noalloc", "tritt_noalloc_scratch_bytes",
 )
 
 _lib = None
@@ -69,6 +69,9 @@ def lib():
                 L.tritt_dps_fwd.argtypes = [vp] * 7 + [i] * 5 + [f] + [i] * 2 + [vp, sz, vp, i, vp]
                 L.tritt_dps_bwd.restype = i
                 L.tritt_dps_bwd.argtypes = [vp] * 13 + [i] * 5 + [f] + [i] * 2 + [vp, sz, vp, i, vp]
+                L.tritt_tdp_fwd_noalloc.restype = i
+                L.tritt_tdp_fwd_noalloc.argtypes = [vp] * 7 + [i] * 5 + [f] + [i] * 5 + [vp, i, vp]
+                L.tritt_noalloc_scratch_bytes.restype = sz
                 L.tritt_selftest_umma.restype = i
                 L.tritt_selftest_umma.argtypes = [vp] * 5 + [i, vp, vp]
                 _lib = L
@@ -198,4 +201,19 @@ def dps_bwd(q, k1, k2, v1, v2, o, do, m, dq, dk1, dk2, dv1, dv2, alpha, causal, 
                                  int(bool(causal)), int(k_diff), ws.data_ptr(), ws.numel(),
                                  status_word(q.device).data_ptr(), flags, _stream())
     _check(rc, "tritt_dps_bwd")
+    launches += 1
+
+
+def tdp_fwd_noalloc(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr, flags=0):
+    """Forward through ``tritt_tdp_fwd_noalloc``: no workspace is passed; the library uses the scratch
+    array built into its device image (for callers that are not allowed to allocate device memory).
+    Calls on one GPU must not overlap in time."""
+    global launches
+    B, N, T, D = q.shape
+    with torch.cuda.device(q.device):
+        rc = lib().tritt_tdp_fwd_noalloc(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
+                                         o.data_ptr(), lse.data_ptr(), B, N, T, D, dtype_code(q.dtype), float(alpha),
+                                         int(bool(causal)), _win(k1w, T), _win(k2w, T), _win(kkl, T), _win(kkr, T),
+                                         status_word(q.device).data_ptr(), flags, _stream())
+    _check(rc, "tritt_tdp_fwd_noalloc")
     launches += 1

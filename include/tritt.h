@@ -119,6 +119,24 @@ int tritt_dps_bwd(const void* q, const void* k1, const void* k2, const void* v1,
                   size_t workspace_bytes, int* status_word, int flags, tritt_stream_t stream);
 
 /*
+ * Triple-dot-product forward for callers that may not allocate device memory (a plugin inside
+ * another program's enqueue hook, a process whose device memory all belongs to a pool this call
+ * site cannot use, a section that must avoid the allocator's device-wide synchronisation).
+ * Same computation and checks as tritt_tdp_fwd for all query rows, but the scratch is an 8 MiB array
+ * built into the library image (tritt_noalloc_scratch_bytes()), held by every GPU that loads the
+ * library until the process exits.  Limits: 16-bit inputs with B*N*T*D > 4 194 304 elements are
+ * rejected (fp32 inputs need no scratch); calls that overlap in time on one GPU share the array and
+ * race; the first call on a device resolves the array's address and should precede any stream
+ * capture on that device.  It calls no allocation routine.  This entry point has no counterpart in
+ * the reference.
+ */
+int tritt_tdp_fwd_noalloc(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, void* o,
+                          float* lse, int B, int N, int T, int D, int dtype, float alpha, int causal,
+                          int k1_window, int k2_window, int kk_left, int kk_right, int* status_word, int flags,
+                          tritt_stream_t stream);
+size_t tritt_noalloc_scratch_bytes(void);
+
+/*
  * Self-test of the tensor-core building blocks (TMA tile loads, shared-memory operand
  * descriptors, a 16-bit operand held in tensor memory): one CTA computes
  *   C = A * Bm^T   and   C2 = round16(C) * V      (all matrices 128 x 128, row-major)
