@@ -79,6 +79,20 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Tile reduce-add from shared memory into global memory (element type and swizzle come from the
+// tensor map; rows outside the tensor are dropped).  Completion is tracked per thread in bulk groups.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   (uint64_t)m),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until the shared-memory source of every committed bulk group of this thread has been read.
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Wait until every committed bulk group of this thread has fully completed (writes performed).
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ------------------------------------------------------------------ TMEM
 // Allocation is warp-collective (all 32 lanes execute it); `ncols` is a power of two >= 32.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
@@ -262,6 +276,9 @@ __device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Same for a 64-byte-swizzled tile whose rows are 64 bytes (chunk 0..3): XOR with (row / 2) mod 4.
+__device__ __forceinline__ uint32_t swz64(uint32_t row, uint32_t chunk) { return row * 64u + ((chunk ^ ((row >> 1) & 3u)) << 4); }
+
 // Byte offset of the 16-byte chunk `chunk` (0..7) of row `row` inside a 128-byte-swizzled
 // tile whose rows are 128 bytes: the chunk index is XOR-ed with (row mod 8).
 __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
@@ -273,5 +290,9 @@ __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t chunk) { retur
 // with the 128-byte swizzle; box = {64 cols, box_rows, 1}.  Out-of-range rows read zero.
 int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t cols, uint64_t rows, uint64_t bn,
                  uint32_t box_cols, uint32_t box_rows);
+// Same over an fp32 tensor (used as the destination of TMA reduce-adds); the swizzle follows the box
+// width (64-byte rows -> 64-byte swizzle, 128-byte rows -> 128-byte swizzle).
+int make_tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t bn, uint32_t box_cols,
+                     uint32_t box_rows);
 
 }  // namespace tritt

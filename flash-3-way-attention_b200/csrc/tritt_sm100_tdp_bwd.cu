@@ -1,7 +1,7 @@
 // Triple-dot-product trittention backward on Blackwell tensor cores (tcgen05 + TMEM + TMA).
 //
 // Same pair-row formulation as the forward kernel.  For one query q and a tile of 128 rows
-// x of a "row" key tensor X (with its value tensor Y), against 64-row slabs of the
+// x of a "row" key tensor X (with its value tensor Y), against 128-row slabs of the
 // "column" key/value tensors Kc / Vc:
 //     A [r,h] = alpha*log2(e) * Q[q,h]  * X[x_r,h]          A'[r,h] = dO[q,h] * Y[x_r,h]
 //     S  = A  Kc^T          P  = exp2(S - lse2[q])          (recomputed from the saved lse)
@@ -13,15 +13,21 @@
 // the two key axes (the score and the gated value are symmetric under the swap): X = K1,
 // Y = SiLU(V1), Kc = K2, Vc = V2, and yields dK1 and dSiLU(V1).  Four GEMM-shaped products per
 // (tile, slab) and role - eight in all against the six of a minimal schedule - but every
-// key-side gradient is owned by rows of a tile, so the only cross-CTA reductions are
-// vector float adds of one 128 x D block per tile into fp32 accumulators.
+// key-side gradient is owned by rows of a tile, so the only cross-CTA reductions are one
+// 128 x D block per tile and tensor, added to fp32 accumulators by TMA reduce-add.
 // (The reference runs one Triton kernel per gradient, recomputing P five times:
 // triple_dot_product/kernels/bwd_dq.py, bwd_dk1.py, bwd_dk2.py, bwd_dv1.py, bwd_dv2.py.)
 //
-// CTA layout (persistent, 256 threads): warp 0 TMA producer, warp 1 tcgen05.mma issuer,
-// warps 4-7 one warpgroup that forms the operands, turns (S, dP) into (P, dS) slab by slab
-// and folds G / U into the gradients.  Work item = (query, head, role); it walks the row
-// tiles x <= q and, inside, the column slabs c <= q.
+// Tensor-core usage follows what the hardware rewards: 128-column slabs, so that every
+// accumulation chain is 8 instructions of 128x128x16 (an instruction below N = 128 costs the same
+// ~48-64 cycles, and every change of accumulator costs the pipe ~120 cycles), TMEM fully used
+// as S | dP | G | U (4 x 128 columns at D = 128).  P and dS are written back as 16-bit into the
+// first half of the S and dP column ranges and feed the G / U products from tensor memory.
+//
+// CTA layout (persistent, 128 + 128*NWG threads): warp 0 TMA producer, warp 1 tcgen05.mma
+// issuer, warps 4.. NWG warpgroups that share every tile: warpgroup g owns 128/NWG columns of each
+// slab and a share of the operand formation and of the gradient fold.  Work item = (query, head,
+// role); it walks the row tiles x <= q and, inside, the column slabs c <= q.
 #include "tritt_sm100_tdp.cuh"
 
 #include <cstdlib>
@@ -34,43 +40,42 @@ __device__ long long g_timing[148 * 16];
 namespace {
 using namespace sm100;
 
-constexpr int kBC = 64;  // key columns per slab
+constexpr int kBC = 128;  // key columns per slab
 
 template <int D> struct BwdCfg {
-  static constexpr int kTileA = 128 * D * 2;
-  static constexpr int kStage = kBC * D * 2;
-  static constexpr int kStages = 8;
-  static constexpr int kOffA = 0;                  // A  (row-key pre-product)
-  static constexpr int kOffA2 = kTileA;            // A' (row-value pre-product)
+  static constexpr int kTileA = 128 * D * 2;   // one 128-row operand / key / value tile
+  static constexpr int kStages = 4;            // ring of column tiles: Kc(c), Vc(c), Kc(c+1), Vc(c+1)
+  static constexpr int kOffA = 0;              // A  (row-key pre-product)
+  static constexpr int kOffA2 = kTileA;        // A' (row-value pre-product)
   static constexpr int kOffRing = 2 * kTileA;
-  static constexpr int kOffRed = kOffRing + kStages * kStage;  // [4][D] fp32 cross-warp sums
-  static constexpr int kOffVec = kOffRed + 4 * D * 4;          // [2][D] fp32: Q[q], dO[q]
-  static constexpr int kSmem = kOffVec + 2 * D * 4 + 1024;
+  static constexpr int kOffStage = kOffRing + kStages * kTileA;  // per-warp 2 KiB slots for the TMA reduce-adds
+  static constexpr int kStageBytes = 16 * 2048;
+  static constexpr int kOffDq = kOffStage + kStageBytes;         // [D] fp32: dQ column sums of the current query
+  static constexpr int kOffVec = kOffDq + D * 4;                 // [2][D] fp32: Q[q], dO[q]
+  static constexpr int kOffMisc = kOffVec + 2 * D * 4;           // [4] fp32: Dq partials
+  static constexpr int kSmem = kOffMisc + 16 + 1024;             // + alignment slack
   static constexpr int kTmemS = 0, kTmemDP = 128, kTmemG = 256, kTmemU = 256 + D;
 };
 
 struct BwdParams {
   const void *q, *o, *d_o;
-  const void *x[2], *y[2];  // row key / value tensors per role (raw pointers, for the epilogue)
+  const void* x[2];  // row key tensor per role (raw pointers, for the dQ fold)
   const float* lse;
   void* dq;
-  float *dX[2], *dY[2];     // fp32 accumulators per role
   int T, BN, nq, q_mod, q_rem, causal;
   float alpha;
   int* status;
 };
 
 struct BwdBarriers {
-  uint64_t ring_full[8], ring_empty[8];
+  uint64_t ring_full[4], ring_empty[4];
   uint64_t xy_full, a_ready, a_free, gu_done;
-  uint64_t sdp_ready[2], pds_ready[2], wg_sync;
+  uint64_t sdp_ready, pds_ready, wg_sync;
   uint32_t tmem_base;
   int abort_flag;
 };
 
 #ifdef TRITT_TIMING
-// Development build only: per-CTA cycle counters of where each role waits.
-
 #define TT_DECL long long tt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tt_t = clock64();
 #define TT(slot) { const long long tt_n = clock64(); tt_acc[slot] += tt_n - tt_t; tt_t = tt_n; }
 #define TT_FLUSH(basei) if (blockIdx.x < 148) { for (int i = 0; i < 8; ++i) g_timing[blockIdx.x * 16 + (basei) + i] = tt_acc[i]; }
@@ -80,17 +85,12 @@ struct BwdBarriers {
 #define TT_FLUSH(basei)
 #endif
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
-
 template <int D, typename T16, int NWG>
 __global__ void __launch_bounds__(128 + 128 * NWG, 1)
 tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__ CUtensorMap tmK2,
                const __grid_constant__ CUtensorMap tmSV1, const __grid_constant__ CUtensorMap tmV2,
-               const __grid_constant__ CUtensorMap tmK1r, const __grid_constant__ CUtensorMap tmK2r,
-               const __grid_constant__ CUtensorMap tmSV1r, const __grid_constant__ CUtensorMap tmV2r, BwdParams p) {
+               const __grid_constant__ CUtensorMap tmDK1, const __grid_constant__ CUtensorMap tmDK2,
+               const __grid_constant__ CUtensorMap tmDSV1, const __grid_constant__ CUtensorMap tmDV2, BwdParams p) {
   using Cfg = BwdCfg<D>;
   constexpr int NS = Cfg::kStages;
   constexpr int KH = D / 64;
@@ -109,10 +109,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     mbar_init(&bars.a_ready, 128 * NWG);
     mbar_init(&bars.a_free, 128 * NWG);
     mbar_init(&bars.gu_done, 1);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&bars.sdp_ready[b], 1);
-      mbar_init(&bars.pds_ready[b], 128 * NWG);
-    }
+    mbar_init(&bars.sdp_ready, 1);
+    mbar_init(&bars.pds_ready, 128 * NWG);
     mbar_init(&bars.wg_sync, 128 * NWG);
     fence_barrier_init();
   }
@@ -144,7 +142,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      const CUtensorMap* maps[8] = {&tmK1, &tmK2, &tmSV1, &tmV2, &tmK1r, &tmK2r, &tmSV1r, &tmV2r};
+      const CUtensorMap* maps[8] = {&tmK1, &tmK2, &tmSV1, &tmV2, &tmDK1, &tmDK2, &tmDSV1, &tmDV2};
       for (int i = 0; i < 8; ++i) tma_prefetch_desc(maps[i]);
       uint32_t xt_count = 0, pos = 0;
       bool alive = true;
@@ -155,10 +153,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         mbar_arrive(&bars.ring_full[st]);
         (void)tm; (void)row0; (void)bh;
 #else
-        mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kStage);
+        mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kTileA);
         for (int hh = 0; hh < KH; ++hh)
-          tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kStage + hh * (kBC * 128), tm, &bars.ring_full[st], hh * 64,
-                      row0, bh);
+          tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kTileA + hh * 16384, tm, &bars.ring_full[st], hh * 64, row0, bh);
 #endif
         ++pos;
         return true;
@@ -170,8 +167,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         // role 0: columns K1 / SiLU(V1), rows K2 / V2;   role 1: columns K2 / V2, rows K1 / SiLU(V1)
         const CUtensorMap* tmKc = role == 0 ? &tmK1 : &tmK2;
         const CUtensorMap* tmVc = role == 0 ? &tmSV1 : &tmV2;
-        const CUtensorMap* tmX = role == 0 ? &tmK2r : &tmK1r;
-        const CUtensorMap* tmY = role == 0 ? &tmV2r : &tmSV1r;
+        const CUtensorMap* tmX = role == 0 ? &tmK2 : &tmK1;
+        const CUtensorMap* tmY = role == 0 ? &tmV2 : &tmSV1;
         for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
           if (!mbar_wait(&bars.a_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
           mbar_arrive_expect_tx(&bars.xy_full, 2 * Cfg::kTileA);
@@ -202,10 +199,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       constexpr uint32_t idesc_g = make_idesc_f16(128, D, kFmt, false, true);
       // descriptor low words; per instruction only a constant (in 16-byte units) is added
       constexpr uint32_t kHi = desc_hi(1024);
-      constexpr uint32_t kStage16 = Cfg::kStage >> 4;
+      constexpr uint32_t kTile16 = Cfg::kTileA >> 4;
       const uint32_t aLo = desc_lo(smem_u32(smem + Cfg::kOffA), 16), a2Lo = desc_lo(smem_u32(smem + Cfg::kOffA2), 16);
-      const uint32_t ringK = desc_lo(smem_u32(smem + Cfg::kOffRing), 16);           // K-major view of a stage
-      const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), kBC * 128);   // row-major (MN-major) view
+      const uint32_t ringK = desc_lo(smem_u32(smem + Cfg::kOffRing), 16);      // K-major view of a stage
+      const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), 16384);  // row-major (MN-major) view
       uint32_t xt_count = 0, base = 0, n = 0;
       bool alive = true;
       TT_DECL
@@ -216,49 +213,46 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         return ok;
       };
       // S(slab) = A Kc^T and dP(slab) = A' Vc^T
-      auto issue_sdp = [&](uint32_t slab_n, uint32_t pos) -> bool {
-        const uint32_t b = slab_n & 1;
+      auto issue_sdp = [&](uint32_t pos) -> bool {
         if (!wait_full(pos)) return false;
         {
-          const uint32_t bLo = ringK + (pos % NS) * kStage16;
+          const uint32_t bLo = ringK + (pos % NS) * kTile16;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
-            const uint32_t ka = (k >> 2) * (16384 >> 4) + (k & 3) * 2, kb = (k >> 2) * ((kBC * 128) >> 4) + (k & 3) * 2;
-            mma_ss_lo(tmem + Cfg::kTmemS + b * kBC, aLo + ka, bLo + kb, kHi, idesc_s, k > 0);
+            const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
+            mma_ss_lo(tmem + Cfg::kTmemS, aLo + kk, bLo + kk, kHi, idesc_s, k > 0);
           }
           TT(4)
         }
         if (!wait_full(pos + 1)) return false;
         {
-          const uint32_t bLo = ringK + ((pos + 1) % NS) * kStage16;
+          const uint32_t bLo = ringK + ((pos + 1) % NS) * kTile16;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
-            const uint32_t ka = (k >> 2) * (16384 >> 4) + (k & 3) * 2, kb = (k >> 2) * ((kBC * 128) >> 4) + (k & 3) * 2;
-            mma_ss_lo(tmem + Cfg::kTmemDP + b * kBC, a2Lo + ka, bLo + kb, kHi, idesc_s, k > 0);
+            const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
+            mma_ss_lo(tmem + Cfg::kTmemDP, a2Lo + kk, bLo + kk, kHi, idesc_s, k > 0);
           }
           TT(5)
         }
-        mma_commit(&bars.sdp_ready[b]);
+        mma_commit(&bars.sdp_ready);
         TT(7)
         return true;
       };
-      // G (+)= dS Kc and U (+)= P Vc, then hand the two ring stages back
-      auto issue_gu = [&](uint32_t slab_n, uint32_t pos, bool accumulate) {
-        const uint32_t b = slab_n & 1;
+      // G (+)= dS Kc and U (+)= P Vc, then hand the two ring stages back.
+      // Warpgroup g packed its CW columns of P into S[g*CW, g*CW + CW/2) and of dS into dP[g*CW, ...).
+      auto issue_gu = [&](uint32_t pos, bool accumulate) {
         const uint32_t stK = pos % NS, stV = (pos + 1) % NS;
-        // Each warpgroup packed its columns of P and dS into its own column range of the S slab:
-        // P in the first half of the range, dS in the second half.
-        constexpr int CW = kBC / NWG, KPW = CW / 16;  // columns, and 16-deep MMA steps, per warpgroup
+        constexpr int CW = kBC / NWG, KPW = CW / 16;
         const uint32_t acc = accumulate ? 1u : 0u;
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
-          const uint32_t a = tmem + Cfg::kTmemS + b * kBC + (k / KPW) * CW + CW / 2 + (k % KPW) * 8;
-          mma_ts_lo(tmem + Cfg::kTmemG, a, ringMN + stK * kStage16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
+          const uint32_t a = tmem + Cfg::kTmemDP + (k / KPW) * CW + (k % KPW) * 8;
+          mma_ts_lo(tmem + Cfg::kTmemG, a, ringMN + stK * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
         }
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
-          const uint32_t a = tmem + Cfg::kTmemS + b * kBC + (k / KPW) * CW + (k % KPW) * 8;
-          mma_ts_lo(tmem + Cfg::kTmemU, a, ringMN + stV * kStage16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
+          const uint32_t a = tmem + Cfg::kTmemS + (k / KPW) * CW + (k % KPW) * 8;
+          mma_ts_lo(tmem + Cfg::kTmemU, a, ringMN + stV * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
         }
         TT(6)
         mma_commit(&bars.ring_empty[stK]);
@@ -275,22 +269,18 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           if (!mbar_wait(&bars.a_ready, xt_count & 1, abort_flag)) { alive = false; break; }
           TT(2)
           tc_fence_after();
-          const uint32_t n0 = n;
-          if (!issue_sdp(n0, base)) { alive = false; break; }
-          if (ncs > 1 && !issue_sdp(n0 + 1, base + 2)) { alive = false; break; }
-          for (int c = 0; c < ncs && alive; ++c) {
-            const uint32_t sn = n0 + c;
+          if (!issue_sdp(base)) { alive = false; break; }
+          for (int c = 0; c < ncs && alive; ++c, ++n) {
             TT(0)
-            if (!mbar_wait(&bars.pds_ready[sn & 1], (sn >> 1) & 1, abort_flag)) { alive = false; break; }
+            if (!mbar_wait(&bars.pds_ready, n & 1, abort_flag)) { alive = false; break; }
             TT(3)
             tc_fence_after();
-            issue_gu(sn, base + 2 * c, c > 0);
-            if (c + 2 < ncs) {
-              if (!issue_sdp(sn + 2, base + 2 * (c + 2))) { alive = false; break; }
+            issue_gu(base + 2 * c, c > 0);
+            if (c + 1 < ncs) {
+              if (!issue_sdp(base + 2 * (c + 1))) { alive = false; break; }
             }
           }
           if (alive) mma_commit(&bars.gu_done);
-          n = n0 + ncs;
           base += 2 * ncs;
         }
       }
@@ -299,17 +289,17 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ soft-max / gradient warpgroups
-    // NWG warpgroups share every tile: warpgroup g owns the columns [g*CW, (g+1)*CW) of each slab and
-    // the head-dimension range [g*HW, (g+1)*HW) of the operand formation and of the gradient fold.
     constexpr int CW = kBC / NWG;   // slab columns per warpgroup
-    constexpr int HW = D / NWG;     // head-dimension columns per warpgroup
+    constexpr int HW = D / NWG;     // head-dimension columns per warpgroup (operand formation)
     const int wg = (warp - 4) >> 2;
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-    float* red = (float*)(smem + Cfg::kOffRed);
+    uint8_t* slot = smem + Cfg::kOffStage + (warp - 4) * 2048;  // this warp's staging slot (32 rows x 16 fp32)
+    float* dq_acc = (float*)(smem + Cfg::kOffDq);
     float* qv = (float*)(smem + Cfg::kOffVec);  // Q[q, :]
     float* dov = qv + D;                        // dO[q, :]
+    float* misc = (float*)(smem + Cfg::kOffMisc);
     uint32_t xt_count = 0, n = 0, wg_phase = 0;
     bool alive = true;
     TT_DECL
@@ -326,8 +316,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       tile_counts(q, nxt, ncs);
       const size_t hb = (size_t)bh * T * D;
       const T16* Xg = (const T16*)p.x[role] + hb;
+      const CUtensorMap* tmDX = role == 0 ? &tmDK2 : &tmDK1;
+      const CUtensorMap* tmDY = role == 0 ? &tmDV2 : &tmDSV1;
       // per-query vectors and scalars
-      if (!wg_sync()) { alive = false; break; }  // previous item's readers of qv / dov / red are done
+      if (!wg_sync()) { alive = false; break; }  // previous item's readers of qv / dov / misc are done
       if (wg == 0) {
         float dq_part = 0.f;
         if (row < D) {
@@ -335,18 +327,17 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           const float dof = to_f(((const T16*)p.d_o)[hb + (size_t)q * D + row]);
           qv[row] = qf;
           dov[row] = dof;
+          dq_acc[row] = 0.f;
           dq_part = dof * to_f(((const T16*)p.o)[hb + (size_t)q * D + row]);
         }
 #pragma unroll
         for (int o = 16; o >= 1; o >>= 1) dq_part += __shfl_xor_sync(0xffffffffu, dq_part, o);
-        if (lane == 0) red[wq] = dq_part;
+        if (lane == 0) misc[wq] = dq_part;
       }
       if (!wg_sync()) { alive = false; break; }
-      const float Dq = red[0] + red[1] + red[2] + red[3];
+      const float Dq = misc[0] + misc[1] + misc[2] + misc[3];
       const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e;
       const float scale2 = p.alpha * kLog2e;
-      float dQ_run = 0.f;  // role 0: thread `row` of warpgroup 0 owns dQ[q, row]
-      if (!wg_sync()) { alive = false; break; }  // red is reused by the tile folds
 
       for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
         // ---- operand formation (in place): A = scale2*Q[q] (.) X tile,  A' = dO[q] (.) Y tile
@@ -380,9 +371,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 
         // ---- slabs: (S, dP) -> (P, dS), this warpgroup's CW columns
         for (int c = 0; c < ncs; ++c, ++n) {
-          const uint32_t b = n & 1;
           TT(2)
-          alive = __all_sync(0xffffffffu, mbar_wait(&bars.sdp_ready[b], (n >> 1) & 1, abort_flag));
+          alive = __all_sync(0xffffffffu, mbar_wait(&bars.sdp_ready, n & 1, abort_flag));
           TT(3)
           if (!alive) break;
           tc_fence_after();
@@ -392,110 +382,120 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             mbar_arrive(&bars.a_free);
           }
           const int cmax = (row_valid ? (p.causal ? q : T - 1) - c * kBC : -1) - wg * CW;
-          const uint32_t tS = tmem + lane_base + Cfg::kTmemS + b * kBC + wg * CW;
-          const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + b * kBC + wg * CW;
+          const uint32_t tS = tmem + lane_base + Cfg::kTmemS + wg * CW;
+          const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + wg * CW;
 #ifndef TRITT_EXP_NOSOFTMAX
-          uint32_t s[CW], dp[CW];
-          tmem_ld(tS, s);
-          tmem_ld(tDP, dp);
-          tmem_wait_ld();
-          uint32_t pk[CW / 2], dk[CW / 2];
-          if (cmax >= CW - 1) {
 #pragma unroll
-            for (int i = 0; i < CW; i += 2) {
-              const float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
-              const float d0 = p0 * (__uint_as_float(dp[i]) - Dq), d1 = p1 * (__uint_as_float(dp[i + 1]) - Dq);
-              pk[i >> 1] = pack2<T16>(p0, p1);
-              dk[i >> 1] = pack2<T16>(d0, d1);
-            }
-          } else {
+          for (int sc = 0; sc < CW / 32; ++sc) {
+            uint32_t s[32], dp[32];
+            tmem_ld32(tS + sc * 32, s);
+            tmem_ld32(tDP + sc * 32, dp);
+            tmem_wait_ld();
+            uint32_t pk[16], dk[16];
+            const int cm = cmax - sc * 32;
+            if (cm >= 31) {
 #pragma unroll
-            for (int i = 0; i < CW; i += 2) {
-              float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
-              if (i > cmax) p0 = 0.f;
-              if (i + 1 > cmax) p1 = 0.f;
-              const float d0 = p0 * (__uint_as_float(dp[i]) - Dq), d1 = p1 * (__uint_as_float(dp[i + 1]) - Dq);
-              pk[i >> 1] = pack2<T16>(p0, p1);
-              dk[i >> 1] = pack2<T16>(d0, d1);
+              for (int i = 0; i < 32; i += 2) {
+                const float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
+                const float d0 = p0 * (__uint_as_float(dp[i]) - Dq), d1 = p1 * (__uint_as_float(dp[i + 1]) - Dq);
+                pk[i >> 1] = pack2<T16>(p0, p1);
+                dk[i >> 1] = pack2<T16>(d0, d1);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
+                if (i > cm) p0 = 0.f;
+                if (i + 1 > cm) p1 = 0.f;
+                const float d0 = p0 * (__uint_as_float(dp[i]) - Dq), d1 = p1 * (__uint_as_float(dp[i + 1]) - Dq);
+                pk[i >> 1] = pack2<T16>(p0, p1);
+                dk[i >> 1] = pack2<T16>(d0, d1);
+              }
             }
+            tmem_st16(tS + sc * 16, pk);    // P  -> S columns this thread has already read
+            tmem_st16(tDP + sc * 16, dk);   // dS -> dP columns this thread has already read
           }
-          tmem_st(tS, pk);            // P  -> first half of this warpgroup's column range
-          tmem_st(tS + CW / 2, dk);   // dS -> second half
           tmem_wait_st();
 #else
           (void)cmax; (void)tS; (void)tDP; (void)lse2; (void)Dq;
 #endif
           tc_fence_before();
-          mbar_arrive(&bars.pds_ready[b]);
+          mbar_arrive(&bars.pds_ready);
         }
         if (!alive) break;
 
-        // ---- fold G / U of this tile into the gradients (32-column chunks dealt round-robin to the warpgroups)
+        // ---- fold G / U of this tile into the gradients: 16-column pieces dealt round-robin to the warps of a
+        // lane quadrant, staged in shared memory (64-byte swizzle) and added to the fp32 accumulators by TMA.
         TT(2)
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.gu_done, xt_count & 1, abort_flag));
         TT(4)
         if (!alive) break;
         tc_fence_after();
-        const bool store_row = row_valid && x_r < T;
-        float* dXr = p.dX[role] + hb + (size_t)x_r * D;
-        float* dYr = p.dY[role] + hb + (size_t)x_r * D;
-#pragma unroll
-        for (int ci = 0; ci < (D / 32 + NWG - 1) / NWG; ++ci) {
-          const int ch = wg + ci * NWG;  // 32-column chunk of the head dimension
-          if (ch >= D / 32) break;
-          uint32_t g[32];
-          tmem_ld32(tmem + lane_base + Cfg::kTmemG + ch * 32, g);
+        const bool x_ok = row_valid && x_r < T;
+        for (int pc = wg; pc < 2 * (D / 16); pc += NWG) {
+          const bool is_u = pc >= D / 16;
+          const int h0 = (is_u ? pc - D / 16 : pc) * 16;
+          uint32_t g[16];
+          tmem_ld16(tmem + lane_base + (is_u ? Cfg::kTmemU : Cfg::kTmemG) + h0, g);
           tmem_wait_ld();
-          float v[32];
+          float v[16];
+          const float* mul = is_u ? dov : qv;
+          const float sc = is_u ? 1.f : p.alpha;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = p.alpha * __uint_as_float(g[i]);
-          if (store_row) {
+          for (int i = 0; i < 16; ++i) v[i] = sc * __uint_as_float(g[i]);
+          bulk_wait_read();  // the previous reduce-add of this warp has finished reading the slot
+          __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const int h = ch * 32 + i;
-              red_add_v4(dXr + h, v[i] * qv[h], v[i + 1] * qv[h + 1], v[i + 2] * qv[h + 2], v[i + 3] * qv[h + 3]);
-            }
+          for (int i4 = 0; i4 < 4; ++i4) {
+            float4 w4 = make_float4(v[i4 * 4] * mul[h0 + i4 * 4], v[i4 * 4 + 1] * mul[h0 + i4 * 4 + 1],
+                                    v[i4 * 4 + 2] * mul[h0 + i4 * 4 + 2], v[i4 * 4 + 3] * mul[h0 + i4 * 4 + 3]);
+            *reinterpret_cast<float4*>(slot + swz64(lane, i4)) = w4;
           }
-          if (role == 0) {
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_3d(is_u ? tmDY : tmDX, slot, h0, xt * 128 + wq * 32, bh);
+            bulk_commit();
+          }
+          if (!is_u && role == 0) {
             // dQ[q,h] += alpha sum_r G[r,h] X[x_r,h]
+            uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+            if (x_ok) {
+              x0 = __ldg(reinterpret_cast<const uint4*>(Xg + (size_t)x_r * D + h0));
+              x1 = __ldg(reinterpret_cast<const uint4*>(Xg + (size_t)x_r * D + h0 + 8));
+            }
+            const uint32_t wx[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-            for (int i4 = 0; i4 < 4; ++i4) {
-              uint4 xv = make_uint4(0, 0, 0, 0);
-              if (store_row) xv = __ldg(reinterpret_cast<const uint4*>(Xg + (size_t)x_r * D + ch * 32 + i4 * 8));
-              const uint32_t wx[4] = {xv.x, xv.y, xv.z, xv.w};
+            for (int e = 0; e < 8; ++e) {
+              const float2 f = unpack2<T16>(wx[e]);
+              v[2 * e] *= f.x;
+              v[2 * e + 1] *= f.y;
+            }
+            // column sums over the 32 rows of this warp: halving butterfly, lane i (< 16) ends with column i
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = unpack2<T16>(wx[e]);
-                v[i4 * 8 + 2 * e] *= f.x;
-                v[i4 * 8 + 2 * e + 1] *= f.y;
+            for (int half = 8; half >= 1; half >>= 1) {
+              const bool upper = lane & half;
+#pragma unroll
+              for (int i = 0; i < half; ++i) {
+                const float keep = upper ? v[i + half] : v[i];
+                const float send = upper ? v[i] : v[i + half];
+                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
               }
             }
-            const float colsum = warp_transpose_sum(v, lane);
-            red[wq * D + ch * 32 + lane] = colsum;
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], 16);
+            if (lane < 16) atomicAdd(&dq_acc[h0 + lane], v[0]);
           }
-          uint32_t u[32];
-          tmem_ld32(tmem + lane_base + Cfg::kTmemU + ch * 32, u);
-          tmem_wait_ld();
-          if (store_row) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const int h = ch * 32 + i;
-              red_add_v4(dYr + h, __uint_as_float(u[i]) * dov[h], __uint_as_float(u[i + 1]) * dov[h + 1],
-                         __uint_as_float(u[i + 2]) * dov[h + 2], __uint_as_float(u[i + 3]) * dov[h + 3]);
-            }
-          }
-        }
-        if (role == 0) {
-          if (!wg_sync()) { alive = false; break; }
-          if (wg == 0 && row < D) dQ_run += red[row] + red[D + row] + red[2 * D + row] + red[3 * D + row];
-          if (!wg_sync()) { alive = false; break; }
         }
         tc_fence_before();  // TMEM reads of G / U precede the next tile's first accumulate
         TT(5)
       }
       if (!alive) break;
-      if (role == 0 && wg == 0 && row < D) ((T16*)p.dq)[hb + (size_t)q * D + row] = from_f<T16>(dQ_run);
+      if (role == 0) {
+        if (!wg_sync()) { alive = false; break; }  // all contributions to dq_acc have landed
+        if (wg == 0 && row < D) ((T16*)p.dq)[hb + (size_t)q * D + row] = from_f<T16>(dq_acc[row]);
+      }
     }
+    bulk_wait_all();  // reduce-adds still in flight must complete before the CTA retires
     if (wg == 0 && row == 0) { TT_FLUSH(8) }
   }
 
@@ -517,23 +517,19 @@ int launch_bwd(const TdpArgs& a) {
   silu_kernel<T16><<<(unsigned)((n / 8 + 255) / 256 + 1), 256, 0, a.stream>>>((const T16*)a.v1, sv1, n);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
-  CUtensorMap tmK1, tmK2, tmSV1, tmV2, tmK1r, tmK2r, tmSV1r, tmV2r;
+  CUtensorMap tmK1, tmK2, tmSV1, tmV2, tmDK1, tmDK2, tmDSV1, tmDV2;
   int rc;
-  if ((rc = make_tmap_3d(&tmK1, a.k1, 2, D, a.T, BN, 64, kBC))) return rc;
-  if ((rc = make_tmap_3d(&tmK2, a.k2, 2, D, a.T, BN, 64, kBC))) return rc;
-  if ((rc = make_tmap_3d(&tmSV1, sv1, 2, D, a.T, BN, 64, kBC))) return rc;
-  if ((rc = make_tmap_3d(&tmV2, a.v2, 2, D, a.T, BN, 64, kBC))) return rc;
-  if ((rc = make_tmap_3d(&tmK1r, a.k1, 2, D, a.T, BN, 64, 128))) return rc;
-  if ((rc = make_tmap_3d(&tmK2r, a.k2, 2, D, a.T, BN, 64, 128))) return rc;
-  if ((rc = make_tmap_3d(&tmSV1r, sv1, 2, D, a.T, BN, 64, 128))) return rc;
-  if ((rc = make_tmap_3d(&tmV2r, a.v2, 2, D, a.T, BN, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmK1, a.k1, 2, D, a.T, BN, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmK2, a.k2, 2, D, a.T, BN, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmSV1, sv1, 2, D, a.T, BN, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmV2, a.v2, 2, D, a.T, BN, 64, 128))) return rc;
+  if ((rc = make_tmap_3d_f32(&tmDK1, part, D, a.T, BN, 16, 32))) return rc;
+  if ((rc = make_tmap_3d_f32(&tmDK2, part + n, D, a.T, BN, 16, 32))) return rc;
+  if ((rc = make_tmap_3d_f32(&tmDSV1, part + 2 * n, D, a.T, BN, 16, 32))) return rc;
+  if ((rc = make_tmap_3d_f32(&tmDV2, part + 3 * n, D, a.T, BN, 16, 32))) return rc;
   BwdParams p{};
   p.q = a.q; p.o = a.o; p.d_o = a.d_o; p.lse = a.lse_in; p.dq = a.dq;
-  p.x[0] = a.k2; p.y[0] = a.v2; p.x[1] = a.k1; p.y[1] = sv1;
-  p.dX[0] = part + n;      // dK2
-  p.dY[0] = part + 3 * n;  // dV2
-  p.dX[1] = part;          // dK1
-  p.dY[1] = part + 2 * n;  // dSiLU(V1)
+  p.x[0] = a.k2; p.x[1] = a.k1;
   p.T = a.T; p.BN = BN; p.q_mod = a.q_mod; p.q_rem = a.q_rem;
   p.nq = a.q_rem < a.T ? (a.T - a.q_rem + a.q_mod - 1) / a.q_mod : 0;
   p.causal = a.mask.causal;
@@ -544,12 +540,27 @@ int launch_bwd(const TdpArgs& a) {
     TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     const long items = (long)p.nq * BN * 2;
     const int grid = (int)(items < num_sms() ? items : num_sms());
-    kern<<<grid, 128 + 128 * NWG, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmK1r, tmK2r, tmSV1r, tmV2r, p);
+    kern<<<grid, 128 + 128 * NWG, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmDK1, tmDK2, tmDSV1, tmDV2, p);
     count_launch();
     TRITT_CUDA_OK(cudaGetLastError());
   }
   if (a.flags & TRITT_FLAG_BWD_PARTIAL) return 0;
   return simt_tdp_bwd_finalize(a.v1, a.dk1, a.dk2, a.dv1, a.dv2, n, a.dtype, part, a.stream);
+}
+
+// Number of soft-max warpgroups per CTA (2 or 4); TRITT_BWD_WG overrides the default for tuning.
+int bwd_warpgroups() {
+  static int v = 0;
+  if (!v) {
+    const char* e = getenv("TRITT_BWD_WG");
+    v = (e && atoi(e) == 2) ? 2 : 4;
+  }
+  return v;
+}
+
+template <int D, typename T16>
+int launch_bwd_wg(const TdpArgs& a) {
+  return bwd_warpgroups() == 2 ? launch_bwd<D, T16, 2>(a) : launch_bwd<D, T16, 4>(a);
 }
 
 }  // namespace
@@ -565,21 +576,6 @@ namespace tritt {
 size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D) {
   const size_t n = (size_t)B * N * T * D;
   return 4 * n * sizeof(float) + n * 2;
-}
-
-// Number of soft-max warpgroups per CTA (2 or 4); TRITT_BWD_WG overrides the default for tuning.
-static int bwd_warpgroups() {
-  static int v = 0;
-  if (!v) {
-    const char* e = getenv("TRITT_BWD_WG");
-    v = (e && atoi(e) == 2) ? 2 : 4;
-  }
-  return v;
-}
-
-template <int D, typename T16>
-static int launch_bwd_wg(const TdpArgs& a) {
-  return bwd_warpgroups() == 2 ? launch_bwd<D, T16, 2>(a) : launch_bwd<D, T16, 4>(a);
 }
 
 int sm100_tdp_bwd(const TdpArgs& a) {
