@@ -24,13 +24,17 @@
 // as S | dP | G | U (4 x 128 columns at D = 128).  P and dS are written back as 16-bit into the
 // first half of the S and dP column ranges and feed the G / U products from tensor memory.
 //
-// CTA layout (persistent, 128 + 128*NWG threads): warp 0 TMA producer, warp 1 tcgen05.mma
-// issuer, warps 4.. NWG warpgroups that share every tile: warpgroup g owns 128/NWG columns of each
-// slab and a share of the operand formation and of the gradient fold.  Work item = (query, head,
-// role); it walks the row tiles x <= q and, inside, the column slabs c <= q.
+// CTA layout (persistent, 512 threads): warp 0 TMA producer, warp 1 tcgen05.mma issuer, warps 4-11 two
+// soft-max warpgroups (64 columns of every slab each; they also form the operands), warps 12-15 the
+// fold warpgroup.  The slab pipeline is split in four hand-offs so that the exponentials (the MUFU
+// bound part) overlap the tensor pipe although S and dP are single-buffered:
+//     MMA:      U(c) S(c+1) | G(c) dP(c+1) | U(c+1) S(c+2) | ...
+//     soft-max:      [S(c+1) -> P(c+1)]  [dP(c+1), P(c+1) -> dS(c+1)]
+// The fold warpgroup drains G / U of tile t (TMEM -> registers -> shared memory -> TMA reduce-add)
+// while the other warps already run tile t+1.  Work item = (query, head, role); it walks the row tiles
+// x <= q and, inside, the column slabs c <= q.
 #include "tritt_sm100_tdp.cuh"
 
-#include <cstdlib>
 #include <type_traits>
 
 namespace tritt {
@@ -48,14 +52,18 @@ template <int D> struct BwdCfg {
   static constexpr int kOffA = 0;              // A  (row-key pre-product)
   static constexpr int kOffA2 = kTileA;        // A' (row-value pre-product)
   static constexpr int kOffRing = 2 * kTileA;
-  static constexpr int kOffStage = kOffRing + kStages * kTileA;  // per-warp 2 KiB slots for the TMA reduce-adds
-  static constexpr int kStageBytes = 16 * 2048;
+  static constexpr int kOffStage = kOffRing + kStages * kTileA;  // fold staging: 4 warps x 2 slots x 4 KiB
+  static constexpr int kStageBytes = 4 * 2 * 4096;
   static constexpr int kOffDq = kOffStage + kStageBytes;         // [D] fp32: dQ column sums of the current query
-  static constexpr int kOffVec = kOffDq + D * 4;                 // [2][D] fp32: Q[q], dO[q]
-  static constexpr int kOffMisc = kOffVec + 2 * D * 4;           // [4] fp32: Dq partials
-  static constexpr int kSmem = kOffMisc + 16 + 1024;             // + alignment slack
+  static constexpr int kOffVec = kOffDq + D * 4;                 // [2 parities][2][D] fp32: Q[q], dO[q]
+  static constexpr int kOffMisc = kOffVec + 4 * D * 4;           // [4] fp32: Dq partials
+  static constexpr int kOffBars = kOffMisc + 16;                 // barriers (no static shared memory is used, so
+  static constexpr int kSmem = kOffBars + 192;                   //  the dynamic region starts 1024-byte aligned)
   static constexpr int kTmemS = 0, kTmemDP = 128, kTmemG = 256, kTmemU = 256 + D;
 };
+
+constexpr int kBwdThreads = 512;
+constexpr int kNumSoftmax = 256;  // threads of the two soft-max warpgroups
 
 struct BwdParams {
   const void *q, *o, *d_o;
@@ -69,8 +77,11 @@ struct BwdParams {
 
 struct BwdBarriers {
   uint64_t ring_full[4], ring_empty[4];
-  uint64_t xy_full, a_ready, a_free, gu_done;
-  uint64_t sdp_ready, pds_ready, wg_sync;
+  uint64_t xy_full, a_ready, a_free;
+  uint64_t s_ready, dp_ready, p_ready, ds_ready;  // slab hand-offs
+  uint64_t gu_done, gu_free;                      // tile hand-offs with the fold warpgroup
+  uint64_t sm_sync, fold_sync;
+  uint64_t vec_free[2];                           // fold warpgroup -> soft-max: a copy of Q[q] / dO[q] is no longer read
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -85,8 +96,8 @@ struct BwdBarriers {
 #define TT_FLUSH(basei)
 #endif
 
-template <int D, typename T16, int NWG>
-__global__ void __launch_bounds__(128 + 128 * NWG, 1)
+template <int D, typename T16>
+__global__ void __launch_bounds__(kBwdThreads, 1)
 tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__ CUtensorMap tmK2,
                const __grid_constant__ CUtensorMap tmSV1, const __grid_constant__ CUtensorMap tmV2,
                const __grid_constant__ CUtensorMap tmDK1, const __grid_constant__ CUtensorMap tmDK2,
@@ -94,10 +105,15 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   using Cfg = BwdCfg<D>;
   constexpr int NS = Cfg::kStages;
   constexpr int KH = D / 64;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ BwdBarriers bars;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  static_assert(sizeof(BwdBarriers) <= 192, "barrier block too large");
+  BwdBarriers& bars = *reinterpret_cast<BwdBarriers*>(smem + Cfg::kOffBars);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (smem_u32(smem) & 1023u) {
+    // swizzled tiles need 1024-byte alignment; uniform over the CTA, so every thread leaves here
+    if (tid == 0 && p.status) atomicOr(p.status, 8);
+    return;
+  }
 
   if (tid == 0) {
     bars.abort_flag = 0;
@@ -106,12 +122,18 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       mbar_init(&bars.ring_empty[i], 1);
     }
     mbar_init(&bars.xy_full, 1);
-    mbar_init(&bars.a_ready, 128 * NWG);
-    mbar_init(&bars.a_free, 128 * NWG);
+    mbar_init(&bars.a_ready, kNumSoftmax);
+    mbar_init(&bars.a_free, kNumSoftmax);
+    mbar_init(&bars.s_ready, 1);
+    mbar_init(&bars.dp_ready, 1);
+    mbar_init(&bars.p_ready, kNumSoftmax);
+    mbar_init(&bars.ds_ready, kNumSoftmax);
     mbar_init(&bars.gu_done, 1);
-    mbar_init(&bars.sdp_ready, 1);
-    mbar_init(&bars.pds_ready, 128 * NWG);
-    mbar_init(&bars.wg_sync, 128 * NWG);
+    mbar_init(&bars.gu_free, 128);
+    mbar_init(&bars.sm_sync, kNumSoftmax);
+    mbar_init(&bars.fold_sync, 128);
+    mbar_init(&bars.vec_free[0], 128);
+    mbar_init(&bars.vec_free[1], 128);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -212,52 +234,52 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         TT(1)
         return ok;
       };
-      // S(slab) = A Kc^T and dP(slab) = A' Vc^T
-      auto issue_sdp = [&](uint32_t pos) -> bool {
+      // One 8-instruction accumulation chain each (D = 128): S = A Kc^T, dP = A' Vc^T (operands in shared
+      // memory, key/value tile K-major), U (+)= P Vc, G (+)= dS Kc (P / dS from tensor memory, the tile row-major).
+      auto issue_s = [&](uint32_t pos) -> bool {
         if (!wait_full(pos)) return false;
-        {
-          const uint32_t bLo = ringK + (pos % NS) * kTile16;
+        const uint32_t bLo = ringK + (pos % NS) * kTile16;
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-            mma_ss_lo(tmem + Cfg::kTmemS, aLo + kk, bLo + kk, kHi, idesc_s, k > 0);
-          }
-          TT(4)
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
+          mma_ss_lo(tmem + Cfg::kTmemS, aLo + kk, bLo + kk, kHi, idesc_s, k > 0);
         }
-        if (!wait_full(pos + 1)) return false;
-        {
-          const uint32_t bLo = ringK + ((pos + 1) % NS) * kTile16;
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-            mma_ss_lo(tmem + Cfg::kTmemDP, a2Lo + kk, bLo + kk, kHi, idesc_s, k > 0);
-          }
-          TT(5)
-        }
-        mma_commit(&bars.sdp_ready);
-        TT(7)
+        mma_commit(&bars.s_ready);
+        TT(4)
         return true;
       };
-      // G (+)= dS Kc and U (+)= P Vc, then hand the two ring stages back.
-      // Warpgroup g packed its CW columns of P into S[g*CW, g*CW + CW/2) and of dS into dP[g*CW, ...).
-      auto issue_gu = [&](uint32_t pos, bool accumulate) {
-        const uint32_t stK = pos % NS, stV = (pos + 1) % NS;
-        constexpr int CW = kBC / NWG, KPW = CW / 16;
-        const uint32_t acc = accumulate ? 1u : 0u;
+      auto issue_dp = [&](uint32_t pos) -> bool {
+        if (!wait_full(pos)) return false;
+        const uint32_t bLo = ringK + (pos % NS) * kTile16;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
+          mma_ss_lo(tmem + Cfg::kTmemDP, a2Lo + kk, bLo + kk, kHi, idesc_s, k > 0);
+        }
+        mma_commit(&bars.dp_ready);
+        TT(5)
+        return true;
+      };
+      // soft-max warpgroup g packed its 64 columns of P into S[64g, 64g+32) and of dS into dP[64g, 64g+32)
+      auto issue_u = [&](uint32_t pos, uint32_t acc) {
+        const uint32_t st = pos % NS;
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
-          const uint32_t a = tmem + Cfg::kTmemDP + (k / KPW) * CW + (k % KPW) * 8;
-          mma_ts_lo(tmem + Cfg::kTmemG, a, ringMN + stK * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
+          const uint32_t a = tmem + Cfg::kTmemS + (k >> 2) * 64 + (k & 3) * 8;
+          mma_ts_lo(tmem + Cfg::kTmemU, a, ringMN + st * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
         }
-#pragma unroll
-        for (int k = 0; k < kBC / 16; ++k) {
-          const uint32_t a = tmem + Cfg::kTmemS + (k / KPW) * CW + (k % KPW) * 8;
-          mma_ts_lo(tmem + Cfg::kTmemU, a, ringMN + stV * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
-        }
+        mma_commit(&bars.ring_empty[st]);
         TT(6)
-        mma_commit(&bars.ring_empty[stK]);
-        mma_commit(&bars.ring_empty[stV]);
-        TT(7)
+      };
+      auto issue_g = [&](uint32_t pos, uint32_t acc) {
+        const uint32_t st = pos % NS;
+#pragma unroll
+        for (int k = 0; k < kBC / 16; ++k) {
+          const uint32_t a = tmem + Cfg::kTmemDP + (k >> 2) * 64 + (k & 3) * 8;
+          mma_ts_lo(tmem + Cfg::kTmemG, a, ringMN + st * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
+        }
+        mma_commit(&bars.ring_empty[st]);
+        TT(6)
       };
 
       for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
@@ -269,16 +291,25 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           if (!mbar_wait(&bars.a_ready, xt_count & 1, abort_flag)) { alive = false; break; }
           TT(2)
           tc_fence_after();
-          if (!issue_sdp(base)) { alive = false; break; }
+          if (!issue_s(base) || !issue_dp(base + 1)) { alive = false; break; }
           for (int c = 0; c < ncs && alive; ++c, ++n) {
+            const bool more = c + 1 < ncs;
             TT(0)
-            if (!mbar_wait(&bars.pds_ready, n & 1, abort_flag)) { alive = false; break; }
+            if (!mbar_wait(&bars.p_ready, n & 1, abort_flag)) { alive = false; break; }
+            if (c == 0) {
+              // the fold warpgroup must have drained the previous tile's G / U
+              if (!mbar_wait(&bars.gu_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+            }
             TT(3)
             tc_fence_after();
-            issue_gu(base + 2 * c, c > 0);
-            if (c + 1 < ncs) {
-              if (!issue_sdp(base + 2 * (c + 1))) { alive = false; break; }
-            }
+            issue_u(base + 2 * c + 1, c > 0);
+            if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
+            TT(0)
+            if (!mbar_wait(&bars.ds_ready, n & 1, abort_flag)) { alive = false; break; }
+            TT(3)
+            tc_fence_after();
+            issue_g(base + 2 * c, c > 0);
+            if (more && !issue_dp(base + 2 * (c + 1) + 1)) { alive = false; break; }
           }
           if (alive) mma_commit(&bars.gu_done);
           base += 2 * ncs;
@@ -287,39 +318,37 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       TT(0)
       TT_FLUSH(0)
     }
-  } else if (warp >= 4) {
-    // ------------------------------------------------------------------ soft-max / gradient warpgroups
-    constexpr int CW = kBC / NWG;   // slab columns per warpgroup
-    constexpr int HW = D / NWG;     // head-dimension columns per warpgroup (operand formation)
-    const int wg = (warp - 4) >> 2;
+  } else if (warp >= 4 && warp < 12) {
+    // ------------------------------------------------------------------ soft-max warpgroups
+    const int wg = (warp - 4) >> 2;            // owns columns [64*wg, 64*wg + 64) of every slab
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
+    const int st = tid - 128;                  // 0..255
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-    uint8_t* slot = smem + Cfg::kOffStage + (warp - 4) * 2048;  // this warp's staging slot (32 rows x 16 fp32)
-    float* dq_acc = (float*)(smem + Cfg::kOffDq);
-    float* qv = (float*)(smem + Cfg::kOffVec);  // Q[q, :]
-    float* dov = qv + D;                        // dO[q, :]
+    float* vec = (float*)(smem + Cfg::kOffVec);
     float* misc = (float*)(smem + Cfg::kOffMisc);
-    uint32_t xt_count = 0, n = 0, wg_phase = 0;
+    uint32_t xt_count = 0, n = 0, sync_phase = 0, item_count = 0;
     bool alive = true;
     TT_DECL
-    auto wg_sync = [&]() -> bool {
-      mbar_arrive(&bars.wg_sync);
-      const bool ok = mbar_wait(&bars.wg_sync, wg_phase & 1, abort_flag);
-      ++wg_phase;
+    auto sm_sync = [&]() -> bool {
+      mbar_arrive(&bars.sm_sync);
+      const bool ok = mbar_wait(&bars.sm_sync, sync_phase & 1, abort_flag);
+      ++sync_phase;
       return __all_sync(0xffffffffu, ok);
     };
 
-    for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+    for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++item_count) {
       int role, bh, q, nxt, ncs;
       decode(item, role, bh, q);
       tile_counts(q, nxt, ncs);
       const size_t hb = (size_t)bh * T * D;
-      const T16* Xg = (const T16*)p.x[role] + hb;
-      const CUtensorMap* tmDX = role == 0 ? &tmDK2 : &tmDK1;
-      const CUtensorMap* tmDY = role == 0 ? &tmDV2 : &tmDSV1;
-      // per-query vectors and scalars
-      if (!wg_sync()) { alive = false; break; }  // previous item's readers of qv / dov / misc are done
+      float* qv = vec + (item_count & 1) * 2 * D;  // Q[q, :] (double-buffered by item: the fold warpgroup of the
+      float* dov = qv + D;                         // dO[q, :]  previous item may still be reading its copy)
+      if (!sm_sync()) { alive = false; break; }    // previous item's readers of misc are done
+      // the fold warpgroup can lag two items behind: wait until it has stopped reading this copy of the vectors
+      alive = __all_sync(0xffffffffu,
+                         mbar_wait(&bars.vec_free[item_count & 1], ((item_count >> 1) & 1) ^ 1, abort_flag));
+      if (!alive) break;
       if (wg == 0) {
         float dq_part = 0.f;
         if (row < D) {
@@ -327,14 +356,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           const float dof = to_f(((const T16*)p.d_o)[hb + (size_t)q * D + row]);
           qv[row] = qf;
           dov[row] = dof;
-          dq_acc[row] = 0.f;
           dq_part = dof * to_f(((const T16*)p.o)[hb + (size_t)q * D + row]);
         }
 #pragma unroll
         for (int o = 16; o >= 1; o >>= 1) dq_part += __shfl_xor_sync(0xffffffffu, dq_part, o);
         if (lane == 0) misc[wq] = dq_part;
       }
-      if (!wg_sync()) { alive = false; break; }
+      if (!sm_sync()) { alive = false; break; }
       const float Dq = misc[0] + misc[1] + misc[2] + misc[3];
       const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e;
       const float scale2 = p.alpha * kLog2e;
@@ -346,8 +374,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         TT(1)
         if (!alive) break;
 #pragma unroll
-        for (int ci = 0; ci < HW / 8; ++ci) {
-          const int cc = wg * (HW / 8) + ci;
+        for (int ci = 0; ci < D / 16; ++ci) {
+          const int cc = wg * (D / 16) + ci;
           const uint32_t off = (cc >> 3) * 16384 + swz128(row, cc & 7);
           uint4 xv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA + off);
           uint4 yv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA2 + off);
@@ -363,140 +391,186 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           *reinterpret_cast<uint4*>(smem + Cfg::kOffA2 + off) = make_uint4(wy[0], wy[1], wy[2], wy[3]);
         }
         fence_async_smem();
-        tc_fence_before();
         mbar_arrive(&bars.a_ready);
 
         const int x_r = xt * 128 + row;
         const bool row_valid = p.causal ? (x_r <= q) : (x_r < T);
+        const uint32_t tS = tmem + lane_base + Cfg::kTmemS + wg * 64;
+        const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + wg * 64;
 
-        // ---- slabs: (S, dP) -> (P, dS), this warpgroup's CW columns
         for (int c = 0; c < ncs; ++c, ++n) {
+          const int cmax = (row_valid ? (p.causal ? q : T - 1) - c * kBC : -1) - wg * 64;
+          uint32_t pk[32];
+          // ---- S -> P
           TT(2)
-          alive = __all_sync(0xffffffffu, mbar_wait(&bars.sdp_ready, n & 1, abort_flag));
+          alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready, n & 1, abort_flag));
+          TT(3)
+          if (!alive) break;
+          tc_fence_after();
+#pragma unroll
+          for (int sc = 0; sc < 2; ++sc) {
+            uint32_t s[32];
+            tmem_ld32(tS + sc * 32, s);
+            tmem_wait_ld();
+            const int cm = cmax - sc * 32;
+            if (cm >= 31) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 2)
+                pk[sc * 16 + (i >> 1)] =
+                    pack2<T16>(exp2f(__uint_as_float(s[i]) - lse2), exp2f(__uint_as_float(s[i + 1]) - lse2));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float p0 = i > cm ? 0.f : exp2f(__uint_as_float(s[i]) - lse2);
+                const float p1 = i + 1 > cm ? 0.f : exp2f(__uint_as_float(s[i + 1]) - lse2);
+                pk[sc * 16 + (i >> 1)] = pack2<T16>(p0, p1);
+              }
+            }
+          }
+          tmem_st32(tS, pk);  // P -> first half of this warpgroup's S columns (all of them already read)
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&bars.p_ready);
+          // ---- dP, P -> dS
+          TT(2)
+          alive = __all_sync(0xffffffffu, mbar_wait(&bars.dp_ready, n & 1, abort_flag));
           TT(3)
           if (!alive) break;
           tc_fence_after();
           if (c == ncs - 1) {
             // every S / dP product of this tile has completed: the operand tiles may be reloaded
-            fence_async_smem();
             mbar_arrive(&bars.a_free);
           }
-          const int cmax = (row_valid ? (p.causal ? q : T - 1) - c * kBC : -1) - wg * CW;
-          const uint32_t tS = tmem + lane_base + Cfg::kTmemS + wg * CW;
-          const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + wg * CW;
-#ifndef TRITT_EXP_NOSOFTMAX
+          uint32_t dk[32];
 #pragma unroll
-          for (int sc = 0; sc < CW / 32; ++sc) {
-            uint32_t s[32], dp[32];
-            tmem_ld32(tS + sc * 32, s);
+          for (int sc = 0; sc < 2; ++sc) {
+            uint32_t dp[32];
             tmem_ld32(tDP + sc * 32, dp);
             tmem_wait_ld();
-            uint32_t pk[16], dk[16];
-            const int cm = cmax - sc * 32;
-            if (cm >= 31) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
-                const float d0 = p0 * (__uint_as_float(dp[i]) - Dq), d1 = p1 * (__uint_as_float(dp[i + 1]) - Dq);
-                pk[i >> 1] = pack2<T16>(p0, p1);
-                dk[i >> 1] = pack2<T16>(d0, d1);
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                float p0 = exp2f(__uint_as_float(s[i]) - lse2), p1 = exp2f(__uint_as_float(s[i + 1]) - lse2);
-                if (i > cm) p0 = 0.f;
-                if (i + 1 > cm) p1 = 0.f;
-                const float d0 = p0 * (__uint_as_float(dp[i]) - Dq), d1 = p1 * (__uint_as_float(dp[i + 1]) - Dq);
-                pk[i >> 1] = pack2<T16>(p0, p1);
-                dk[i >> 1] = pack2<T16>(d0, d1);
-              }
+            for (int i = 0; i < 32; i += 2) {
+              const float2 pp = unpack2<T16>(pk[sc * 16 + (i >> 1)]);
+              dk[sc * 16 + (i >> 1)] =
+                  pack2<T16>(pp.x * (__uint_as_float(dp[i]) - Dq), pp.y * (__uint_as_float(dp[i + 1]) - Dq));
             }
-            tmem_st16(tS + sc * 16, pk);    // P  -> S columns this thread has already read
-            tmem_st16(tDP + sc * 16, dk);   // dS -> dP columns this thread has already read
           }
+          tmem_st32(tDP, dk);  // dS -> first half of this warpgroup's dP columns
           tmem_wait_st();
-#else
-          (void)cmax; (void)tS; (void)tDP; (void)lse2; (void)Dq;
-#endif
           tc_fence_before();
-          mbar_arrive(&bars.pds_ready);
+          mbar_arrive(&bars.ds_ready);
         }
         if (!alive) break;
-
-        // ---- fold G / U of this tile into the gradients: 16-column pieces dealt round-robin to the warps of a
-        // lane quadrant, staged in shared memory (64-byte swizzle) and added to the fp32 accumulators by TMA.
-        TT(2)
+      }
+    }
+    if (wg == 0 && row == 0) { TT_FLUSH(8) }
+    (void)st;
+  } else if (warp >= 12) {
+    // ------------------------------------------------------------------ fold warpgroup
+    // Drains G / U of a finished tile: 32-column pieces -> registers -> scaled by Q[q] / dO[q] -> shared memory
+    // (128-byte swizzle) -> TMA reduce-add into the fp32 accumulators; for role 0 also dQ[q] += sum_r G X.
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+    uint8_t* slots = smem + Cfg::kOffStage + wq * 8192;  // two 4 KiB slots of this warp
+    float* dq_acc = (float*)(smem + Cfg::kOffDq);
+    float* vec = (float*)(smem + Cfg::kOffVec);
+    uint32_t xt_count = 0, sync_phase = 0, item_count = 0, round = 0;
+    bool alive = true;
+    auto fold_sync = [&]() -> bool {
+      mbar_arrive(&bars.fold_sync);
+      const bool ok = mbar_wait(&bars.fold_sync, sync_phase & 1, abort_flag);
+      ++sync_phase;
+      return __all_sync(0xffffffffu, ok);
+    };
+    for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++item_count) {
+      int role, bh, q, nxt, ncs;
+      decode(item, role, bh, q);
+      tile_counts(q, nxt, ncs);
+      const size_t hb = (size_t)bh * T * D;
+      const T16* Xg = (const T16*)p.x[role] + hb;
+      const CUtensorMap* tmDX = role == 0 ? &tmDK2 : &tmDK1;
+      const CUtensorMap* tmDY = role == 0 ? &tmDV2 : &tmDSV1;
+      const float* qv = vec + (item_count & 1) * 2 * D;
+      const float* dov = qv + D;
+      if (role == 0) {
+        if (row < D) dq_acc[row] = 0.f;
+        if (!fold_sync()) { alive = false; break; }
+      }
+      for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
+        const int x_r = xt * 128 + row;
+        const bool x_ok = (p.causal ? (x_r <= q) : true) && x_r < T;
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.gu_done, xt_count & 1, abort_flag));
-        TT(4)
         if (!alive) break;
         tc_fence_after();
-        const bool x_ok = row_valid && x_r < T;
-        for (int pc = wg; pc < 2 * (D / 16); pc += NWG) {
-          const bool is_u = pc >= D / 16;
-          const int h0 = (is_u ? pc - D / 16 : pc) * 16;
-          uint32_t g[16];
-          tmem_ld16(tmem + lane_base + (is_u ? Cfg::kTmemU : Cfg::kTmemG) + h0, g);
-          tmem_wait_ld();
-          float v[16];
-          const float* mul = is_u ? dov : qv;
-          const float sc = is_u ? 1.f : p.alpha;
+#pragma unroll 1
+        for (int pc = 0; pc < 2 * (D / 32); ++pc, ++round) {
+          const bool is_u = pc >= D / 32;
+          const int h0 = (is_u ? pc - D / 32 : pc) * 32;
+          // role 0, G pieces: this row's X values for the dQ product (issued early to hide the latency)
+          uint4 xr[4];
+          const bool want_dq = !is_u && role == 0;
+          if (want_dq) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = sc * __uint_as_float(g[i]);
-          bulk_wait_read();  // the previous reduce-add of this warp has finished reading the slot
+            for (int i4 = 0; i4 < 4; ++i4)
+              xr[i4] = x_ok ? __ldg(reinterpret_cast<const uint4*>(Xg + (size_t)x_r * D + h0 + i4 * 8))
+                            : make_uint4(0, 0, 0, 0);
+          }
+          uint32_t g[32];
+          tmem_ld32(tmem + lane_base + (is_u ? Cfg::kTmemU : Cfg::kTmemG) + h0, g);
+          tmem_wait_ld();
+          // scale by Q[q] / dO[q] right away: after the hand-off below the soft-max warps may move on to a
+          // later query and overwrite an older copy of these vectors
+          float v[32];
+          {
+            const float* mul = is_u ? dov : qv;
+            const float sc = is_u ? 1.f : p.alpha;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = sc * __uint_as_float(g[i]) * mul[h0 + i];
+          }
+          if (pc == 2 * (D / 32) - 1) {
+            // last piece of this tile is in registers: the accumulators may be overwritten
+            tc_fence_before();
+            mbar_arrive(&bars.gu_free);
+            if (xt == nxt - 1) mbar_arrive(&bars.vec_free[item_count & 1]);  // and this query's vectors are done with
+          }
+          uint8_t* slot = slots + (round & 1) * 4096;
+          // the reduce-add issued two rounds ago from this slot must have finished reading it
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           __syncwarp();
 #pragma unroll
-          for (int i4 = 0; i4 < 4; ++i4) {
-            float4 w4 = make_float4(v[i4 * 4] * mul[h0 + i4 * 4], v[i4 * 4 + 1] * mul[h0 + i4 * 4 + 1],
-                                    v[i4 * 4 + 2] * mul[h0 + i4 * 4 + 2], v[i4 * 4 + 3] * mul[h0 + i4 * 4 + 3]);
-            *reinterpret_cast<float4*>(slot + swz64(lane, i4)) = w4;
-          }
+          for (int i4 = 0; i4 < 8; ++i4)
+            *reinterpret_cast<float4*>(slot + swz128(lane, i4)) =
+                make_float4(v[i4 * 4], v[i4 * 4 + 1], v[i4 * 4 + 2], v[i4 * 4 + 3]);
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
             tma_reduce_add_3d(is_u ? tmDY : tmDX, slot, h0, xt * 128 + wq * 32, bh);
             bulk_commit();
           }
-          if (!is_u && role == 0) {
-            // dQ[q,h] += alpha sum_r G[r,h] X[x_r,h]
-            uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-            if (x_ok) {
-              x0 = __ldg(reinterpret_cast<const uint4*>(Xg + (size_t)x_r * D + h0));
-              x1 = __ldg(reinterpret_cast<const uint4*>(Xg + (size_t)x_r * D + h0 + 8));
-            }
-            const uint32_t wx[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+          if (want_dq) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float2 f = unpack2<T16>(wx[e]);
-              v[2 * e] *= f.x;
-              v[2 * e + 1] *= f.y;
-            }
-            // column sums over the 32 rows of this warp: halving butterfly, lane i (< 16) ends with column i
+            for (int i4 = 0; i4 < 4; ++i4) {
+              const uint32_t wx[4] = {xr[i4].x, xr[i4].y, xr[i4].z, xr[i4].w};
 #pragma unroll
-            for (int half = 8; half >= 1; half >>= 1) {
-              const bool upper = lane & half;
-#pragma unroll
-              for (int i = 0; i < half; ++i) {
-                const float keep = upper ? v[i + half] : v[i];
-                const float send = upper ? v[i] : v[i + half];
-                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack2<T16>(wx[e]);
+                v[i4 * 8 + 2 * e] = p.alpha * __uint_as_float(g[i4 * 8 + 2 * e]) * f.x;
+                v[i4 * 8 + 2 * e + 1] = p.alpha * __uint_as_float(g[i4 * 8 + 2 * e + 1]) * f.y;
               }
             }
-            v[0] += __shfl_xor_sync(0xffffffffu, v[0], 16);
-            if (lane < 16) atomicAdd(&dq_acc[h0 + lane], v[0]);
+            const float colsum = warp_transpose_sum(v, lane);
+            atomicAdd(&dq_acc[h0 + lane], colsum);
           }
         }
-        tc_fence_before();  // TMEM reads of G / U precede the next tile's first accumulate
-        TT(5)
       }
       if (!alive) break;
       if (role == 0) {
-        if (!wg_sync()) { alive = false; break; }  // all contributions to dq_acc have landed
-        if (wg == 0 && row < D) ((T16*)p.dq)[hb + (size_t)q * D + row] = from_f<T16>(dq_acc[row]);
+        if (!fold_sync()) { alive = false; break; }  // every warp's contribution to dq_acc has landed
+        if (row < D) ((T16*)p.dq)[hb + (size_t)q * D + row] = from_f<T16>(dq_acc[row]);
+        if (!fold_sync()) { alive = false; break; }  // dq_acc may be cleared for the next item
       }
     }
     bulk_wait_all();  // reduce-adds still in flight must complete before the CTA retires
-    if (wg == 0 && row == 0) { TT_FLUSH(8) }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -506,7 +580,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   if (tid == 0 && bars.abort_flag && p.status) atomicOr(p.status, 4);
 }
 
-template <int D, typename T16, int NWG>
+template <int D, typename T16>
 int launch_bwd(const TdpArgs& a) {
   using Cfg = BwdCfg<D>;
   const int BN = a.B * a.N;
@@ -523,10 +597,10 @@ int launch_bwd(const TdpArgs& a) {
   if ((rc = make_tmap_3d(&tmK2, a.k2, 2, D, a.T, BN, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tmSV1, sv1, 2, D, a.T, BN, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tmV2, a.v2, 2, D, a.T, BN, 64, 128))) return rc;
-  if ((rc = make_tmap_3d_f32(&tmDK1, part, D, a.T, BN, 16, 32))) return rc;
-  if ((rc = make_tmap_3d_f32(&tmDK2, part + n, D, a.T, BN, 16, 32))) return rc;
-  if ((rc = make_tmap_3d_f32(&tmDSV1, part + 2 * n, D, a.T, BN, 16, 32))) return rc;
-  if ((rc = make_tmap_3d_f32(&tmDV2, part + 3 * n, D, a.T, BN, 16, 32))) return rc;
+  if ((rc = make_tmap_3d_f32(&tmDK1, part, D, a.T, BN, 32, 32))) return rc;
+  if ((rc = make_tmap_3d_f32(&tmDK2, part + n, D, a.T, BN, 32, 32))) return rc;
+  if ((rc = make_tmap_3d_f32(&tmDSV1, part + 2 * n, D, a.T, BN, 32, 32))) return rc;
+  if ((rc = make_tmap_3d_f32(&tmDV2, part + 3 * n, D, a.T, BN, 32, 32))) return rc;
   BwdParams p{};
   p.q = a.q; p.o = a.o; p.d_o = a.d_o; p.lse = a.lse_in; p.dq = a.dq;
   p.x[0] = a.k2; p.x[1] = a.k1;
@@ -536,31 +610,16 @@ int launch_bwd(const TdpArgs& a) {
   p.alpha = a.alpha;
   p.status = a.status_word;
   if (p.nq > 0) {
-    auto kern = tdp_bwd_kernel<D, T16, NWG>;
+    auto kern = tdp_bwd_kernel<D, T16>;
     TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     const long items = (long)p.nq * BN * 2;
     const int grid = (int)(items < num_sms() ? items : num_sms());
-    kern<<<grid, 128 + 128 * NWG, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmDK1, tmDK2, tmDSV1, tmDV2, p);
+    kern<<<grid, kBwdThreads, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmDK1, tmDK2, tmDSV1, tmDV2, p);
     count_launch();
     TRITT_CUDA_OK(cudaGetLastError());
   }
   if (a.flags & TRITT_FLAG_BWD_PARTIAL) return 0;
   return simt_tdp_bwd_finalize(a.v1, a.dk1, a.dk2, a.dv1, a.dv2, n, a.dtype, part, a.stream);
-}
-
-// Number of soft-max warpgroups per CTA (2 or 4); TRITT_BWD_WG overrides the default for tuning.
-int bwd_warpgroups() {
-  static int v = 0;
-  if (!v) {
-    const char* e = getenv("TRITT_BWD_WG");
-    v = (e && atoi(e) == 2) ? 2 : 4;
-  }
-  return v;
-}
-
-template <int D, typename T16>
-int launch_bwd_wg(const TdpArgs& a) {
-  return bwd_warpgroups() == 2 ? launch_bwd<D, T16, 2>(a) : launch_bwd<D, T16, 4>(a);
 }
 
 }  // namespace
@@ -580,8 +639,8 @@ size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D) {
 
 int sm100_tdp_bwd(const TdpArgs& a) {
   if (a.dtype == TRITT_BF16)
-    return a.D == 128 ? launch_bwd_wg<128, __nv_bfloat16>(a) : launch_bwd_wg<64, __nv_bfloat16>(a);
-  return a.D == 128 ? launch_bwd_wg<128, __half>(a) : launch_bwd_wg<64, __half>(a);
+    return a.D == 128 ? launch_bwd<128, __nv_bfloat16>(a) : launch_bwd<64, __nv_bfloat16>(a);
+  return a.D == 128 ? launch_bwd<128, __half>(a) : launch_bwd<64, __half>(a);
 }
 
 }  // namespace tritt
