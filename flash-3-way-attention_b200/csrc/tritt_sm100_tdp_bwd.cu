@@ -35,6 +35,7 @@
 // x <= q and, inside, the column slabs c <= q.
 #include "tritt_sm100_tdp.cuh"
 
+#include <cstdlib>
 #include <type_traits>
 
 namespace tritt {
@@ -62,8 +63,12 @@ template <int D> struct BwdCfg {
   static constexpr int kTmemS = 0, kTmemDP = 128, kTmemG = 256, kTmemU = 256 + D;
 };
 
-constexpr int kBwdThreads = 512;
-constexpr int kNumSoftmax = 256;  // threads of the two soft-max warpgroups
+// NSW soft-max warpgroups (2 or 4) + 4 service warps (TMA, MMA, 2 idle) + the fold warpgroup
+template <int NSW> struct BwdThreads {
+  static constexpr int kSoftmax = 128 * NSW;
+  static constexpr int kTotal = 128 + kSoftmax + 128;
+  static constexpr int kFoldWarp0 = 4 + 4 * NSW;  // first warp of the fold warpgroup (a multiple of 4)
+};
 
 struct BwdParams {
   const void *q, *o, *d_o;
@@ -96,8 +101,8 @@ struct BwdBarriers {
 #define TT_FLUSH(basei)
 #endif
 
-template <int D, typename T16>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+template <int D, typename T16, int NSW>
+__global__ void __launch_bounds__(BwdThreads<NSW>::kTotal, 1)
 tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__ CUtensorMap tmK2,
                const __grid_constant__ CUtensorMap tmSV1, const __grid_constant__ CUtensorMap tmV2,
                const __grid_constant__ CUtensorMap tmDK1, const __grid_constant__ CUtensorMap tmDK2,
@@ -105,6 +110,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   using Cfg = BwdCfg<D>;
   constexpr int NS = Cfg::kStages;
   constexpr int KH = D / 64;
+  constexpr int kNumSoftmax = BwdThreads<NSW>::kSoftmax;
+  constexpr int kFoldWarp0 = BwdThreads<NSW>::kFoldWarp0;
+  constexpr int CW = kBC / NSW;  // slab columns owned by one soft-max warpgroup
   extern __shared__ __align__(1024) uint8_t smem[];
   static_assert(sizeof(BwdBarriers) <= 192, "barrier block too large");
   BwdBarriers& bars = *reinterpret_cast<BwdBarriers*>(smem + Cfg::kOffBars);
@@ -260,12 +268,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         TT(5)
         return true;
       };
-      // soft-max warpgroup g packed its 64 columns of P into S[64g, 64g+32) and of dS into dP[64g, 64g+32)
+      // soft-max warpgroup g packed its CW columns of P into S[CW*g, CW*g + CW/2) and of dS into dP[CW*g, ...)
+      constexpr int KPW = CW / 16;  // 16-deep MMA steps per warpgroup
       auto issue_u = [&](uint32_t pos, uint32_t acc) {
         const uint32_t st = pos % NS;
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
-          const uint32_t a = tmem + Cfg::kTmemS + (k >> 2) * 64 + (k & 3) * 8;
+          const uint32_t a = tmem + Cfg::kTmemS + (k / KPW) * CW + (k % KPW) * 8;
           mma_ts_lo(tmem + Cfg::kTmemU, a, ringMN + st * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
         }
         mma_commit(&bars.ring_empty[st]);
@@ -275,7 +284,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         const uint32_t st = pos % NS;
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
-          const uint32_t a = tmem + Cfg::kTmemDP + (k >> 2) * 64 + (k & 3) * 8;
+          const uint32_t a = tmem + Cfg::kTmemDP + (k / KPW) * CW + (k % KPW) * 8;
           mma_ts_lo(tmem + Cfg::kTmemG, a, ringMN + st * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
         }
         mma_commit(&bars.ring_empty[st]);
@@ -318,12 +327,11 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       TT(0)
       TT_FLUSH(0)
     }
-  } else if (warp >= 4 && warp < 12) {
+  } else if (warp >= 4 && warp < kFoldWarp0) {
     // ------------------------------------------------------------------ soft-max warpgroups
-    const int wg = (warp - 4) >> 2;            // owns columns [64*wg, 64*wg + 64) of every slab
+    const int wg = (warp - 4) >> 2;            // owns columns [CW*wg, CW*wg + CW) of every slab
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
-    const int st = tid - 128;                  // 0..255
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     float* vec = (float*)(smem + Cfg::kOffVec);
     float* misc = (float*)(smem + Cfg::kOffMisc);
@@ -374,8 +382,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         TT(1)
         if (!alive) break;
 #pragma unroll
-        for (int ci = 0; ci < D / 16; ++ci) {
-          const int cc = wg * (D / 16) + ci;
+        for (int ci = 0; ci < D / 8 / NSW; ++ci) {
+          const int cc = wg * (D / 8 / NSW) + ci;
           const uint32_t off = (cc >> 3) * 16384 + swz128(row, cc & 7);
           uint4 xv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA + off);
           uint4 yv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA2 + off);
@@ -395,39 +403,39 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 
         const int x_r = xt * 128 + row;
         const bool row_valid = p.causal ? (x_r <= q) : (x_r < T);
-        const uint32_t tS = tmem + lane_base + Cfg::kTmemS + wg * 64;
-        const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + wg * 64;
+        const uint32_t tS = tmem + lane_base + Cfg::kTmemS + wg * CW;
+        const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + wg * CW;
 
         for (int c = 0; c < ncs; ++c, ++n) {
-          const int cmax = (row_valid ? (p.causal ? q : T - 1) - c * kBC : -1) - wg * 64;
-          uint32_t pk[32];
+          const int cmax = (row_valid ? (p.causal ? q : T - 1) - c * kBC : -1) - wg * CW;
+          uint32_t pk[CW / 2];
           // ---- S -> P
           TT(2)
           alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready, n & 1, abort_flag));
           TT(3)
           if (!alive) break;
           tc_fence_after();
+          {
+            uint32_t s[CW];
 #pragma unroll
-          for (int sc = 0; sc < 2; ++sc) {
-            uint32_t s[32];
-            tmem_ld32(tS + sc * 32, s);
+            for (int sc = 0; sc < CW / 32; ++sc) tmem_ld32(tS + sc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[sc * 32]));
             tmem_wait_ld();
-            const int cm = cmax - sc * 32;
-            if (cm >= 31) {
+            TT(4)
+            if (cmax >= CW - 1) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 2)
-                pk[sc * 16 + (i >> 1)] =
-                    pack2<T16>(exp2f(__uint_as_float(s[i]) - lse2), exp2f(__uint_as_float(s[i + 1]) - lse2));
+              for (int i = 0; i < CW; i += 2)
+                pk[i >> 1] = pack2<T16>(exp2f(__uint_as_float(s[i]) - lse2), exp2f(__uint_as_float(s[i + 1]) - lse2));
             } else {
 #pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const float p0 = i > cm ? 0.f : exp2f(__uint_as_float(s[i]) - lse2);
-                const float p1 = i + 1 > cm ? 0.f : exp2f(__uint_as_float(s[i + 1]) - lse2);
-                pk[sc * 16 + (i >> 1)] = pack2<T16>(p0, p1);
+              for (int i = 0; i < CW; i += 2) {
+                const float p0 = i > cmax ? 0.f : exp2f(__uint_as_float(s[i]) - lse2);
+                const float p1 = i + 1 > cmax ? 0.f : exp2f(__uint_as_float(s[i + 1]) - lse2);
+                pk[i >> 1] = pack2<T16>(p0, p1);
               }
             }
+            TT(5)
           }
-          tmem_st32(tS, pk);  // P -> first half of this warpgroup's S columns (all of them already read)
+          tmem_st(tS, pk);  // P -> first half of this warpgroup's S columns (all of them already read)
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(&bars.p_ready);
@@ -441,20 +449,21 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             // every S / dP product of this tile has completed: the operand tiles may be reloaded
             mbar_arrive(&bars.a_free);
           }
-          uint32_t dk[32];
+          uint32_t dk[CW / 2];
+          {
+            uint32_t dp[CW];
 #pragma unroll
-          for (int sc = 0; sc < 2; ++sc) {
-            uint32_t dp[32];
-            tmem_ld32(tDP + sc * 32, dp);
+            for (int sc = 0; sc < CW / 32; ++sc) tmem_ld32(tDP + sc * 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[sc * 32]));
             tmem_wait_ld();
+            TT(6)
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float2 pp = unpack2<T16>(pk[sc * 16 + (i >> 1)]);
-              dk[sc * 16 + (i >> 1)] =
-                  pack2<T16>(pp.x * (__uint_as_float(dp[i]) - Dq), pp.y * (__uint_as_float(dp[i + 1]) - Dq));
+            for (int i = 0; i < CW; i += 2) {
+              const float2 pp = unpack2<T16>(pk[i >> 1]);
+              dk[i >> 1] = pack2<T16>(pp.x * (__uint_as_float(dp[i]) - Dq), pp.y * (__uint_as_float(dp[i + 1]) - Dq));
             }
+            TT(7)
           }
-          tmem_st32(tDP, dk);  // dS -> first half of this warpgroup's dP columns
+          tmem_st(tDP, dk);  // dS -> first half of this warpgroup's dP columns
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(&bars.ds_ready);
@@ -463,8 +472,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       }
     }
     if (wg == 0 && row == 0) { TT_FLUSH(8) }
-    (void)st;
-  } else if (warp >= 12) {
+  } else if (warp >= kFoldWarp0) {
     // ------------------------------------------------------------------ fold warpgroup
     // Drains G / U of a finished tile: 32-column pieces -> registers -> scaled by Q[q] / dO[q] -> shared memory
     // (128-byte swizzle) -> TMA reduce-add into the fp32 accumulators; for role 0 also dQ[q] += sum_r G X.
@@ -580,7 +588,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   if (tid == 0 && bars.abort_flag && p.status) atomicOr(p.status, 4);
 }
 
-template <int D, typename T16>
+template <int D, typename T16, int NSW>
 int launch_bwd(const TdpArgs& a) {
   using Cfg = BwdCfg<D>;
   const int BN = a.B * a.N;
@@ -610,16 +618,31 @@ int launch_bwd(const TdpArgs& a) {
   p.alpha = a.alpha;
   p.status = a.status_word;
   if (p.nq > 0) {
-    auto kern = tdp_bwd_kernel<D, T16>;
+    auto kern = tdp_bwd_kernel<D, T16, NSW>;
     TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     const long items = (long)p.nq * BN * 2;
     const int grid = (int)(items < num_sms() ? items : num_sms());
-    kern<<<grid, kBwdThreads, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmDK1, tmDK2, tmDSV1, tmDV2, p);
+    kern<<<grid, BwdThreads<NSW>::kTotal, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmDK1, tmDK2, tmDSV1, tmDV2, p);
     count_launch();
     TRITT_CUDA_OK(cudaGetLastError());
   }
   if (a.flags & TRITT_FLAG_BWD_PARTIAL) return 0;
   return simt_tdp_bwd_finalize(a.v1, a.dk1, a.dk2, a.dv1, a.dv2, n, a.dtype, part, a.stream);
+}
+
+// Soft-max warpgroups per CTA: 4 by default; TRITT_BWD_WG=2 selects the 2-warpgroup build (tuning aid).
+int bwd_warpgroups() {
+  static int v = 0;
+  if (!v) {
+    const char* e = getenv("TRITT_BWD_WG");
+    v = (e && atoi(e) == 2) ? 2 : 4;
+  }
+  return v;
+}
+
+template <int D, typename T16>
+int launch_bwd_any(const TdpArgs& a) {
+  return bwd_warpgroups() == 2 ? launch_bwd<D, T16, 2>(a) : launch_bwd<D, T16, 4>(a);
 }
 
 }  // namespace
@@ -639,8 +662,8 @@ size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D) {
 
 int sm100_tdp_bwd(const TdpArgs& a) {
   if (a.dtype == TRITT_BF16)
-    return a.D == 128 ? launch_bwd<128, __nv_bfloat16>(a) : launch_bwd<64, __nv_bfloat16>(a);
-  return a.D == 128 ? launch_bwd<128, __half>(a) : launch_bwd<64, __half>(a);
+    return a.D == 128 ? launch_bwd_any<128, __nv_bfloat16>(a) : launch_bwd_any<64, __nv_bfloat16>(a);
+  return a.D == 128 ? launch_bwd_any<128, __half>(a) : launch_bwd_any<64, __half>(a);
 }
 
 }  // namespace tritt
