@@ -11,17 +11,19 @@
 // b200/fwd_b200.py:217-220,253,317-321, with 16x16 query/key tiles; its generic kernel
 // builds K1 x K2 outer products per tile, triple_dot_product/kernels/fwd.py:160-164.)
 //
-// One CTA (persistent, 384 threads) processes a pair of queries (qa, qb) of the same
-// 64-row block as two concurrent row tiles that share every K1 / SiLU(V1) tile:
-//   warp 0      TMA producer: K2/V2 tile per k-tile, then a ring of 64-row K1 and SiLU(V1) tiles
-//   warp 1      issues tcgen05.mma: S = A*K1^T (operands in shared memory) into a
-//               double-buffered 128x64 fp32 TMEM slab per tile, and acc += P*SiLU(V1) with P
-//               read from TMEM and the value tile used row-major (MN-major descriptor)
-//   warps 4-7   soft-max warpgroup of tile a (one row per thread), warps 8-11 of tile b:
-//               exp2 with lazy rescaling, P written back to TMEM as 16-bit, per-k-tile
-//               fold into the query's running (max, sum, output) and the final store.
+// One CTA (persistent, 512 threads) processes a pair of queries (qa, qb) of the same 128-row
+// block as two row tiles that share every K1 / SiLU(V1) tile and take turns on the tensor pipe:
+//   warp 0       TMA producer: the K2 tile of each k-tile, then a ring of 128-row K1 / SiLU(V1) tiles
+//   warp 1       issues tcgen05.mma: S_x = A_x*K1^T (128x128 fp32 slab in TMEM, one per tile) and
+//                acc_x += P_x*SiLU(V1) with P_x read from TMEM (it overlays S_x) and the value tile used
+//                row-major (MN-major descriptor).  128-column slabs keep every accumulation chain at
+//                8 instructions of 128x128x16, the shape the pipe runs at full rate.
+//   warps 4-7    soft-max warpgroup of tile a (one row per thread), warps 8-11 of tile b: row max,
+//                exp2 with lazy rescaling, P written back to TMEM as 16-bit; they also form A_a, A_b
+//   warps 12-15  fold warpgroup: when a k-tile is finished, folds acc_x (times V2, soft-max over k) into
+//                the queries' running (max, sum, output) while the other warps start the next k-tile
 // Causal structure: for a fixed query the mask is "j <= q" on columns and "k <= q" on rows, so
-// whole j-tiles above q are never visited, only the last j-tile is masked (by a column bound that
+// whole slabs above q are never visited, only the last slab is masked (by a column bound that
 // is uniform over the rows), and rows with k > q get weight zero in the fold.
 #include "tritt_common.cuh"
 #include "tritt_sm100.cuh"
@@ -33,37 +35,39 @@ namespace tritt {
 namespace {
 using namespace sm100;
 
-constexpr int kThreads = 384;
-constexpr int kBJ = 64;           // key columns per MMA slab
+constexpr int kThreads = 512;
+constexpr int kBJ = 128;            // key columns per slab
 constexpr float kRescaleGap = 8.f;  // rescale the accumulator only when the row max grew by more than 2^8
 
 template <int D> struct FwdCfg {
-  static constexpr int kTileA = 128 * D * 2;    // bytes of one 128-row operand tile
-  static constexpr int kStage = kBJ * D * 2;    // bytes of one 64-row K1 / SiLU(V1) tile
-  static constexpr int kStages = D == 128 ? 6 : 8;
+  static constexpr int kTileA = 128 * D * 2;    // bytes of one 128-row tile (operand, K1 or SiLU(V1))
+  static constexpr int kStages = 4;
   static constexpr int kOffAa = 0;
   static constexpr int kOffAb = kTileA;
-  static constexpr int kOffV2 = 2 * kTileA;
-  static constexpr int kOffRing = 3 * kTileA;
-  static constexpr int kOffRed = kOffRing + kStages * kStage;  // [2][4][D] fp32 cross-warp sums
-  static constexpr int kOffStat = kOffRed + 2 * 4 * D * 4;    // [2][8] fp32 cross-warp max / sum
-  static constexpr int kSmem = kOffStat + 2 * 8 * 4 + 1024;   // + alignment slack
-  static constexpr int kTmemO = 256;                          // accumulators start after the 4 score slabs
+  static constexpr int kOffRing = 2 * kTileA;
+  static constexpr int kOffStats = kOffRing + kStages * kTileA;  // [2 parities][2 tiles][128][2] fp32: row (max, sum)
+  static constexpr int kOffRed = kOffStats + 2 * 2 * 128 * 2 * 4;  // [2 tiles][4 warps][D] fp32 column sums
+  static constexpr int kOffFstat = kOffRed + 2 * 4 * D * 4;        // [2 tiles][8] fp32 warp max / sum
+  static constexpr int kOffBars = kOffFstat + 2 * 8 * 4;
+  static constexpr int kSmem = kOffBars + 256;
+  static constexpr int kTmemO = 256;  // S_a | S_b | acc_a | acc_b
 };
 
 struct FwdParams {
   void* out;
   float* lse;
-  const void* q;
+  const void *q, *v2;
   int T, BN, nq, q_mod, q_rem, causal, n_pairs;
   float scale2;  // alpha * log2(e)
   int* status;
 };
 
-struct Barriers {
-  uint64_t ring_full[8], ring_empty[8];
+struct FwdBarriers {
+  uint64_t ring_full[4], ring_empty[4];
   uint64_t k2_full, a_ready, a_free;
-  uint64_t s_ready[2][2], p_ready[2][2], pv_done[2], wg_sync[2];
+  uint64_t s_ready[2], p_ready[2];               // per tile, one phase per slab
+  uint64_t o_done, o_free[2], stats_ready[2];    // per k-tile hand-offs with the fold warpgroup
+  uint64_t fold_sync;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -71,14 +75,19 @@ struct Barriers {
 template <int D, typename T16>
 __global__ void __launch_bounds__(kThreads, 1)
 tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__ CUtensorMap tmK2,
-               const __grid_constant__ CUtensorMap tmSV1, const __grid_constant__ CUtensorMap tmV2, FwdParams p) {
+               const __grid_constant__ CUtensorMap tmSV1, FwdParams p) {
   using Cfg = FwdCfg<D>;
   constexpr int NS = Cfg::kStages;
   constexpr int KH = D / 64;  // 64-column halves per row
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ Barriers bars;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  static_assert(sizeof(FwdBarriers) <= 256, "barrier block too large");
+  FwdBarriers& bars = *reinterpret_cast<FwdBarriers*>(smem + Cfg::kOffBars);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (smem_u32(smem) & 1023u) {
+    // swizzled tiles need 1024-byte alignment; uniform over the CTA, so every thread leaves here
+    if (tid == 0 && p.status) atomicOr(p.status, 8);
+    return;
+  }
 
   if (tid == 0) {
     bars.abort_flag = 0;
@@ -90,13 +99,13 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     mbar_init(&bars.a_ready, 256);
     mbar_init(&bars.a_free, 256);
     for (int x = 0; x < 2; ++x) {
-      for (int b = 0; b < 2; ++b) {
-        mbar_init(&bars.s_ready[x][b], 1);
-        mbar_init(&bars.p_ready[x][b], 128);
-      }
-      mbar_init(&bars.pv_done[x], 1);
-      mbar_init(&bars.wg_sync[x], 128);
+      mbar_init(&bars.s_ready[x], 1);
+      mbar_init(&bars.p_ready[x], 128);
+      mbar_init(&bars.o_free[x], 128);
+      mbar_init(&bars.stats_ready[x], 128);
     }
+    mbar_init(&bars.o_done, 1);
+    mbar_init(&bars.fold_sync, 128);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -132,16 +141,14 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       tma_prefetch_desc(&tmK1);
       tma_prefetch_desc(&tmK2);
       tma_prefetch_desc(&tmSV1);
-      tma_prefetch_desc(&tmV2);
       uint32_t kt_count = 0, pos = 0;
       bool alive = true;
       auto load_stage = [&](const CUtensorMap* tm, int row0, int bh) -> bool {
         const int st = pos % NS;
         if (!mbar_wait(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag)) return false;
-        mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kStage);
+        mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kTileA);
         for (int hh = 0; hh < KH; ++hh)
-          tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kStage + hh * (kBJ * 128), tm, &bars.ring_full[st], hh * 64,
-                      row0, bh);
+          tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kTileA + hh * 16384, tm, &bars.ring_full[st], hh * 64, row0, bh);
         ++pos;
         return true;
       };
@@ -150,18 +157,16 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         decode(item, bh, qa, qb);
         tile_counts(qa, qb, nkt, njt);
         for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
-          // the first K1 tiles do not depend on the previous k-tile being folded: fetch them first
+          // the first K1 tile does not depend on the previous k-tile: fetch it before waiting for the operand buffer
           alive = load_stage(&tmK1, 0, bh);
-          if (alive && njt > 1) alive = load_stage(&tmK1, kBJ, bh);
           if (!alive || !mbar_wait(&bars.a_free, (kt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
-          mbar_arrive_expect_tx(&bars.k2_full, 2 * Cfg::kTileA);
-          for (int hh = 0; hh < KH; ++hh) {
+          mbar_arrive_expect_tx(&bars.k2_full, Cfg::kTileA);
+          for (int hh = 0; hh < KH; ++hh)
             tma_load_3d(smem + Cfg::kOffAa + hh * 16384, &tmK2, &bars.k2_full, hh * 64, kt * 128, bh);
-            tma_load_3d(smem + Cfg::kOffV2 + hh * 16384, &tmV2, &bars.k2_full, hh * 64, kt * 128, bh);
-          }
+          // ring order: K1(0), V(0), K1(1), V(1), ...
           for (int jt = 0; jt < njt && alive; ++jt) {
             alive = load_stage(&tmSV1, jt * kBJ, bh);
-            if (alive && jt + 2 < njt) alive = load_stage(&tmK1, (jt + 2) * kBJ, bh);
+            if (alive && jt + 1 < njt) alive = load_stage(&tmK1, (jt + 1) * kBJ, bh);
           }
         }
       }
@@ -183,35 +188,32 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       constexpr uint32_t idesc_pv = make_idesc_f16(128, D, kFmt, false, true);
       // descriptor low words; per instruction only a constant (in 16-byte units) is added
       constexpr uint32_t kHi = desc_hi(1024);
-      constexpr uint32_t kStage16 = Cfg::kStage >> 4;
+      constexpr uint32_t kTile16 = Cfg::kTileA >> 4;
       const uint32_t aLo[2] = {desc_lo(smem_u32(smem + Cfg::kOffAa), 16), desc_lo(smem_u32(smem + Cfg::kOffAb), 16)};
-      const uint32_t ringK = desc_lo(smem_u32(smem + Cfg::kOffRing), 16);          // K-major view of a stage
-      const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), kBJ * 128);  // row-major (MN-major) view
-      uint32_t kt_count = 0, base = 0, n = 0;  // n: score slabs issued per tile so far
+      const uint32_t ringK = desc_lo(smem_u32(smem + Cfg::kOffRing), 16);      // K-major view of a stage
+      const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), 16384);  // row-major (MN-major) view
+      uint32_t kt_count = 0, base = 0, n = 0;  // n: slabs finished so far (same for both tiles)
       bool alive = true;
-      // S_x(slab) = A_x * K1tile^T
-      auto issue_s = [&](int x, uint32_t slab_n, uint32_t pos) {
-        const uint32_t bLo = ringK + (pos % NS) * kStage16;
-        const uint32_t d = tmem + (x * 2 + (slab_n & 1)) * kBJ;
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t ka = (k >> 2) * (16384 >> 4) + (k & 3) * 2, kb = (k >> 2) * ((kBJ * 128) >> 4) + (k & 3) * 2;
-          mma_ss_lo(d, aLo[x] + ka, bLo + kb, kHi, idesc_s, k > 0);
-        }
-        mma_commit(&bars.s_ready[x][slab_n & 1]);
-      };
-      // acc_x (+)= P_x(slab) * SiLU(V1)tile
-      auto issue_pv = [&](int x, uint32_t slab_n, uint32_t pos, bool accumulate) {
-        const uint32_t bLo = ringMN + (pos % NS) * kStage16;
-        const uint32_t a = tmem + (x * 2 + (slab_n & 1)) * kBJ;
-        const uint32_t d = tmem + Cfg::kTmemO + x * D;
-        const uint32_t acc = accumulate ? 1u : 0u;
-#pragma unroll
-        for (int k = 0; k < kBJ / 16; ++k) mma_ts_lo(d, a + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv, k > 0 ? 1u : acc);
-        mma_commit(&bars.pv_done[x]);
-      };
       auto wait_full = [&](uint32_t pos) { return mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag); };
       auto release = [&](uint32_t pos) { mma_commit(&bars.ring_empty[pos % NS]); };
+      // S_x = A_x * K1tile^T  (one chain of D/16 instructions)
+      auto issue_s = [&](int x, uint32_t pos) {
+        const uint32_t bLo = ringK + (pos % NS) * kTile16;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
+          mma_ss_lo(tmem + x * kBJ, aLo[x] + kk, bLo + kk, kHi, idesc_s, k > 0);
+        }
+        mma_commit(&bars.s_ready[x]);
+      };
+      // acc_x (+)= P_x * SiLU(V1)tile  (one chain of 8 instructions; P_x overlays the first 64 columns of S_x)
+      auto issue_pv = [&](int x, uint32_t pos, uint32_t acc) {
+        const uint32_t bLo = ringMN + (pos % NS) * kTile16;
+#pragma unroll
+        for (int k = 0; k < kBJ / 16; ++k)
+          mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv,
+                    k > 0 ? 1u : acc);
+      };
 
       for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
         int bh, qa, qb, nkt, njt;
@@ -220,66 +222,45 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
           if (!mbar_wait(&bars.a_ready, kt_count & 1, abort_flag)) { alive = false; break; }
           tc_fence_after();
-          uint32_t pos = base;
-          const uint32_t n0 = n;
-          // first two score slabs of both tiles
-          if (!wait_full(pos)) { alive = false; break; }
-          issue_s(0, n0, pos);
-          issue_s(1, n0, pos);
-          release(pos);
-          ++pos;
-          if (njt > 1) {
-            if (!wait_full(pos)) { alive = false; break; }
-            issue_s(0, n0 + 1, pos);
-            issue_s(1, n0 + 1, pos);
-            release(pos);
-            ++pos;
-          }
-          for (int jt = 0; jt < njt && alive; ++jt) {
-            const uint32_t pv = pos++;
-            const bool more = jt + 2 < njt;
-            const uint32_t pk = more ? pos++ : 0;
-            const uint32_t sn = n0 + jt;
+          if (!wait_full(base)) { alive = false; break; }
+          issue_s(0, base);
+          issue_s(1, base);
+          release(base);
+          for (int jt = 0; jt < njt && alive; ++jt, ++n) {
+            const uint32_t pv = base + 2 * jt + 1, pk = base + 2 * jt + 2;
+            const bool more = jt + 1 < njt;
             for (int x = 0; x < 2 && alive; ++x) {
-              if (!mbar_wait(&bars.p_ready[x][sn & 1], (sn >> 1) & 1, abort_flag)) { alive = false; break; }
-              tc_fence_after();
-              if (x == 0) {
-                if (!wait_full(pv)) { alive = false; break; }
+              if (!mbar_wait(&bars.p_ready[x], n & 1, abort_flag)) { alive = false; break; }
+              if (jt == 0) {
+                // the fold warpgroup must have drained the previous k-tile's accumulator of this tile
+                if (!mbar_wait(&bars.o_free[x], (kt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
               }
-              issue_pv(x, sn, pv, jt > 0);
+              tc_fence_after();
+              if (x == 0 && !wait_full(pv)) { alive = false; break; }
+              issue_pv(x, pv, jt > 0);
               if (x == 1) release(pv);
               if (more) {
-                if (x == 0) {
-                  if (!wait_full(pk)) { alive = false; break; }
-                }
-                issue_s(x, sn + 2, pk);
+                if (x == 0 && !wait_full(pk)) { alive = false; break; }
+                issue_s(x, pk);
                 if (x == 1) release(pk);
               }
             }
           }
-          n = n0 + njt;
-          base = pos;
+          if (alive) mma_commit(&bars.o_done);
+          base += 2 * njt;
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < 12) {
     // ------------------------------------------------------------------ soft-max warpgroups
     const int x = (warp - 4) >> 2;          // tile: 0 = query a, 1 = query b
     const int wq = warp & 3;                // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;         // row of the tile owned by this thread
     const int st = tid - 128;               // 0..255 over both warpgroups
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-    float* red = (float*)(smem + Cfg::kOffRed) + x * 4 * D;
-    float* stat = (float*)(smem + Cfg::kOffStat) + x * 8;
-    uint32_t kt_count = 0, n = 0, wg_phase = 0;
+    float* stats = (float*)(smem + Cfg::kOffStats);
+    uint32_t kt_count = 0, n = 0;
     bool alive = true;
-    // warpgroup-wide rendezvous with a bounded wait
-    auto wg_sync = [&]() -> bool {
-      mbar_arrive(&bars.wg_sync[x]);
-      const bool ok = mbar_wait(&bars.wg_sync[x], wg_phase & 1, abort_flag);
-      ++wg_phase;
-      return __all_sync(0xffffffffu, ok);
-    };
 
     for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
       int bh, qa, qb, nkt, njt;
@@ -287,8 +268,6 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       tile_counts(qa, qb, nkt, njt);
       const int qx = x == 0 ? qa : qb;
       const T16* Qg = (const T16*)p.q + (size_t)bh * T * D;
-      // running state of the query's output; thread `row` of the warpgroup owns column h = row
-      float M_run = -INFINITY, L_run = 0.f, O_run = 0.f;
 
       for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
         // ---- operand formation: A_a = s*Q[qa] (.) K2tile (in place), A_b = s*Q[qb] (.) K2tile
@@ -322,45 +301,48 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           }
         }
         fence_async_smem();   // generic-proxy stores above -> visible to the tensor core's reads
-        tc_fence_before();    // this thread's TMEM loads of the previous fold precede the next MMAs
         mbar_arrive(&bars.a_ready);
 
-        // ---- walk over the j-tiles
+        // ---- walk over the slabs
+        const uint32_t tS = tmem + lane_base + x * kBJ;
         float m_used = -INFINITY, l_sum = 0.f;
         for (int jt = 0; jt < njt; ++jt, ++n) {
-          const uint32_t buf = n & 1;
-          alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x][buf], (n >> 1) & 1, abort_flag));
+          alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x], n & 1, abort_flag));
           if (!alive) break;
           tc_fence_after();
-          const uint32_t tS = tmem + lane_base + (x * 2 + buf) * kBJ;
-          uint32_t sr[64];
-          tmem_ld64(tS, sr);
-          tmem_wait_ld();
+          if (jt == njt - 1) mbar_arrive(&bars.a_free);  // the last score product of this k-tile has read A_x
           // column bound: j <= q (causal) / j < T
           const int cmax = (p.causal ? qx : T - 1) - jt * kBJ;
-          if (cmax < kBJ - 1) {
+          // pass 1: row maximum
+          float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < kBJ; ++c)
-              if (c > cmax) sr[c] = 0xff800000u;  // -inf
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t sr[64];
+            tmem_ld64(tS + hf * 64, sr);
+            tmem_wait_ld();
+            const int cm = cmax - hf * 64;
+            if (cm >= 63) {
+#pragma unroll
+              for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+            } else {
+#pragma unroll
+              for (int c = 0; c < 64; ++c)
+                if (c <= cm) mx = fmaxf(mx, __uint_as_float(sr[c]));
+            }
           }
-          float mx = __uint_as_float(sr[0]);
-#pragma unroll
-          for (int c = 1; c < kBJ; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
           if (jt == 0) {
             m_used = mx;  // nothing accumulated yet in this k-tile
           } else {
             const bool grow = mx > m_used + kRescaleGap;
             if (__any_sync(0xffffffffu, grow)) {
               // some row of this warp moved its max up noticeably: rescale accumulator rows (factor 1
-              // for the rows that did not move).  The previous P*V must have landed first.
+              // for the rows that did not move).
               const float corr = grow ? exp2f(m_used - mx) : 1.f;
               if (grow) {
                 m_used = mx;
                 l_sum *= corr;
               }
-              alive = __all_sync(0xffffffffu, mbar_wait(&bars.pv_done[x], (n - 1) & 1, abort_flag));
-              if (!alive) break;
-              tc_fence_after();
+              // (s_ready of this slab was committed after the previous P*V, so that product has landed)
               const uint32_t tO = tmem + lane_base + Cfg::kTmemO + x * D;
 #pragma unroll
               for (int ch = 0; ch < D / 32; ++ch) {
@@ -373,90 +355,169 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
               }
             }
           }
+          // pass 2: P = exp2(S - m), packed to 16 bits over the columns already consumed
           float psum = 0.f;
-          uint32_t pk[32];
 #pragma unroll
-          for (int c = 0; c < kBJ; c += 2) {
-            const float p0 = exp2f(__uint_as_float(sr[c]) - m_used), p1 = exp2f(__uint_as_float(sr[c + 1]) - m_used);
-            psum += p0 + p1;
-            pk[c >> 1] = pack2<T16>(p0, p1);
-          }
-          l_sum += psum;
-          if (jt > 0) {
-            // Observe every completion of pv_done in order (a parity wait must never fall two
-            // phases behind); by now the previous P*V has normally long finished.
-            alive = __all_sync(0xffffffffu, mbar_wait(&bars.pv_done[x], (n - 1) & 1, abort_flag));
-            if (!alive) break;
-          }
-          tmem_st32(tS, pk);
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(&bars.p_ready[x][buf]);
-        }
-        if (!alive) break;
-
-        // ---- fold this k-tile into the query's running output
-        alive = __all_sync(0xffffffffu, mbar_wait(&bars.pv_done[x], (n - 1) & 1, abort_flag));
-        if (!alive) break;
-        tc_fence_after();
-        const int k_r = kt * 128 + row;
-        const bool valid = p.causal ? (k_r <= qx) : (k_r < T);
-        float wm = valid ? m_used : -INFINITY;
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-        if (lane == 0) stat[wq] = wm;
-        if (!wg_sync()) { alive = false; break; }
-        const float Mt = fmaxf(fmaxf(stat[0], stat[1]), fmaxf(stat[2], stat[3]));  // finite: row k0 <= q is valid
-        const float w = valid ? exp2f(m_used - Mt) : 0.f;
-        float lw = w * l_sum;
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, o);
-        if (lane == 0) stat[4 + wq] = lw;
-        {
-          const uint32_t tO = tmem + lane_base + Cfg::kTmemO + x * D;
-#pragma unroll
-          for (int ch = 0; ch < D / 32; ++ch) {
-            uint32_t o[32];
-            tmem_ld32(tO + ch * 32, o);
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t sr[64];
+            tmem_ld64(tS + hf * 64, sr);
             tmem_wait_ld();
-            float v[32];
+            const int cm = cmax - hf * 64;
+            uint32_t pk[32];
+            if (cm >= 63) {
 #pragma unroll
-            for (int i4 = 0; i4 < 4; ++i4) {
-              const uint32_t off = (ch >> 1) * 16384 + swz128(row, (ch & 1) * 4 + i4);
-              const uint4 vv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffV2 + off);
-              const uint32_t wv[4] = {vv.x, vv.y, vv.z, vv.w};
+              for (int c = 0; c < 64; c += 2) {
+                const float p0 = exp2f(__uint_as_float(sr[c]) - m_used), p1 = exp2f(__uint_as_float(sr[c + 1]) - m_used);
+                psum += p0 + p1;
+                pk[c >> 1] = pack2<T16>(p0, p1);
+              }
+            } else {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = unpack2<T16>(wv[e]);
-                v[i4 * 8 + 2 * e] = __uint_as_float(o[i4 * 8 + 2 * e]) * (w * f.x);
-                v[i4 * 8 + 2 * e + 1] = __uint_as_float(o[i4 * 8 + 2 * e + 1]) * (w * f.y);
+              for (int c = 0; c < 64; c += 2) {
+                const float p0 = c <= cm ? exp2f(__uint_as_float(sr[c]) - m_used) : 0.f;
+                const float p1 = c + 1 <= cm ? exp2f(__uint_as_float(sr[c + 1]) - m_used) : 0.f;
+                psum += p0 + p1;
+                pk[c >> 1] = pack2<T16>(p0, p1);
               }
             }
-            const float colsum = warp_transpose_sum(v, lane);
-            red[wq * D + ch * 32 + lane] = colsum;
+            tmem_st32(tS + hf * 32, pk);
           }
+          l_sum += psum;
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&bars.p_ready[x]);
         }
-        if (!wg_sync()) { alive = false; break; }
+        if (!alive) break;
+        // ---- hand this k-tile's row statistics to the fold warpgroup
         {
-          const float Lt = stat[4] + stat[5] + stat[6] + stat[7];
-          const float Mn = fmaxf(M_run, Mt);
-          const float ca = exp2f(M_run - Mn), cb = exp2f(Mt - Mn);
-          if (row < D) {
-            const float Ot = red[row] + red[D + row] + red[2 * D + row] + red[3 * D + row];
-            O_run = O_run * ca + Ot * cb;
-          }
-          L_run = L_run * ca + Lt * cb;
-          M_run = Mn;
+          float* srow = stats + (((kt_count & 1) * 2 + x) * 128 + row) * 2;
+          srow[0] = m_used;
+          srow[1] = l_sum;
         }
-        if (!wg_sync()) { alive = false; break; }  // red / stat may be rewritten by the next k-tile
-        fence_async_smem();  // V2 tile reads above precede the next TMA write of that buffer
-        tc_fence_before();
-        mbar_arrive(&bars.a_free);
+        mbar_arrive(&bars.stats_ready[x]);
       }
       if (!alive) break;
-      // ---- store the query's output row and log-sum-exp
-      if (row < D) ((T16*)p.out)[((size_t)bh * T + qx) * D + row] = from_f<T16>(O_run / L_run);
-      if (row == 0) p.lse[(size_t)bh * T + qx] = (M_run + log2f(L_run)) * kLn2;
+    }
+  } else if (warp >= 12) {
+    // ------------------------------------------------------------------ fold warpgroup
+    // After the last P*V of a k-tile: O[q_x,h] accumulates sum_r w_r acc_x[r,h] V2[k_r,h] with
+    // w_r = 2^(m_r - M) over the valid rows, merged into the query's running (max, sum, output).
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+    const float* stats = (const float*)(smem + Cfg::kOffStats);
+    float* red = (float*)(smem + Cfg::kOffRed);      // [2][4][D]
+    float* fstat = (float*)(smem + Cfg::kOffFstat);  // [2][8]
+    uint32_t kt_count = 0, sync_phase = 0;
+    bool alive = true;
+    auto fold_sync = [&]() -> bool {
+      mbar_arrive(&bars.fold_sync);
+      const bool ok = mbar_wait(&bars.fold_sync, sync_phase & 1, abort_flag);
+      ++sync_phase;
+      return __all_sync(0xffffffffu, ok);
+    };
+    for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+      int bh, qa, qb, nkt, njt;
+      decode(item, bh, qa, qb);
+      tile_counts(qa, qb, nkt, njt);
+      const T16* V2g = (const T16*)p.v2 + (size_t)bh * T * D;
+      // running state per tile; thread `row` (< D) owns output column h = row
+      float M_run[2] = {-INFINITY, -INFINITY}, L_run[2] = {0.f, 0.f}, O_run[2] = {0.f, 0.f};
+      for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
+        const int k_r = kt * 128 + row;
+        const uint32_t par = kt_count & 1;
+        // row statistics of both tiles
+        float m_r[2], l_r[2];
+        bool valid[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          alive = alive && __all_sync(0xffffffffu, mbar_wait(&bars.stats_ready[x], par, abort_flag));
+          if (!alive) break;
+          const float* srow = stats + ((par * 2 + x) * 128 + row) * 2;
+          m_r[x] = srow[0];
+          l_r[x] = srow[1];
+          const int qx = x == 0 ? qa : qb;
+          valid[x] = p.causal ? (k_r <= qx) : (k_r < T);
+          float wm = valid[x] ? m_r[x] : -INFINITY;
+#pragma unroll
+          for (int o = 16; o >= 1; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+          if (lane == 0) fstat[x * 8 + wq] = wm;
+        }
+        if (!alive) break;
+        if (!fold_sync()) { alive = false; break; }
+        float Mt[2], w[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          // finite: row k0 of the tile is always valid
+          Mt[x] = fmaxf(fmaxf(fstat[x * 8], fstat[x * 8 + 1]), fmaxf(fstat[x * 8 + 2], fstat[x * 8 + 3]));
+          w[x] = valid[x] ? exp2f(m_r[x] - Mt[x]) : 0.f;
+          float lw = w[x] * l_r[x];
+#pragma unroll
+          for (int o = 16; o >= 1; o >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, o);
+          if (lane == 0) fstat[x * 8 + 4 + wq] = lw;
+        }
+        // accumulators: the last P*V of both tiles must have landed
+        alive = __all_sync(0xffffffffu, mbar_wait(&bars.o_done, par, abort_flag));
+        if (!alive) break;
+        tc_fence_after();
+        const bool in_range = k_r < T;
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          // this row's V2 values for the chunk (shared by both tiles)
+          float v2f[32];
+#pragma unroll
+          for (int i4 = 0; i4 < 4; ++i4) {
+            const uint4 vv = in_range ? __ldg(reinterpret_cast<const uint4*>(V2g + (size_t)k_r * D + ch * 32 + i4 * 8))
+                                      : make_uint4(0, 0, 0, 0);
+            const uint32_t wv[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack2<T16>(wv[e]);
+              v2f[i4 * 8 + 2 * e] = f.x;
+              v2f[i4 * 8 + 2 * e + 1] = f.y;
+            }
+          }
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            uint32_t o[32];
+            tmem_ld32(tmem + lane_base + Cfg::kTmemO + x * D + ch * 32, o);
+            tmem_wait_ld();
+            if (ch == D / 32 - 1) {
+              // last chunk of this tile's accumulator is in registers: it may be overwritten
+              tc_fence_before();
+              mbar_arrive(&bars.o_free[x]);
+            }
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]) * (w[x] * v2f[i]);
+            const float colsum = warp_transpose_sum(v, lane);
+            red[(x * 4 + wq) * D + ch * 32 + lane] = colsum;
+          }
+        }
+        if (!fold_sync()) { alive = false; break; }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const float Lt = fstat[x * 8 + 4] + fstat[x * 8 + 5] + fstat[x * 8 + 6] + fstat[x * 8 + 7];
+          const float Mn = fmaxf(M_run[x], Mt[x]);
+          const float ca = exp2f(M_run[x] - Mn), cb = exp2f(Mt[x] - Mn);
+          if (row < D) {
+            const float Ot = red[(x * 4) * D + row] + red[(x * 4 + 1) * D + row] + red[(x * 4 + 2) * D + row] +
+                             red[(x * 4 + 3) * D + row];
+            O_run[x] = O_run[x] * ca + Ot * cb;
+          }
+          L_run[x] = L_run[x] * ca + Lt * cb;
+          M_run[x] = Mn;
+        }
+        if (!fold_sync()) { alive = false; break; }  // red / fstat are rewritten by the next k-tile
+      }
+      if (!alive) break;
+      // ---- store the two output rows and their log-sum-exp
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        const int qx = x == 0 ? qa : qb;
+        if (row < D) ((T16*)p.out)[((size_t)bh * T + qx) * D + row] = from_f<T16>(O_run[x] / L_run[x]);
+        if (row == 0) p.lse[(size_t)bh * T + qx] = (M_run[x] + log2f(L_run[x])) * kLn2;
+      }
     }
   }
 
@@ -476,16 +537,16 @@ int launch_fwd(const TdpArgs& a) {
   silu_kernel<T16><<<(unsigned)((n / 8 + 255) / 256 + 1), 256, 0, a.stream>>>((const T16*)a.v1, sv1, n);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
-  CUtensorMap tmK1, tmK2, tmSV1, tmV2;
+  CUtensorMap tmK1, tmK2, tmSV1;
   int rc;
-  if ((rc = make_tmap_3d(&tmK1, a.k1, 2, D, a.T, BN, 64, kBJ))) return rc;
-  if ((rc = make_tmap_3d(&tmSV1, sv1, 2, D, a.T, BN, 64, kBJ))) return rc;
+  if ((rc = make_tmap_3d(&tmK1, a.k1, 2, D, a.T, BN, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmSV1, sv1, 2, D, a.T, BN, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tmK2, a.k2, 2, D, a.T, BN, 64, 128))) return rc;
-  if ((rc = make_tmap_3d(&tmV2, a.v2, 2, D, a.T, BN, 64, 128))) return rc;
   FwdParams p{};
   p.out = a.out_o;
   p.lse = a.out_lse;
   p.q = a.q;
+  p.v2 = a.v2;
   p.T = a.T;
   p.BN = BN;
   p.q_mod = a.q_mod;
@@ -500,7 +561,7 @@ int launch_fwd(const TdpArgs& a) {
   TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
   const long items = (long)p.n_pairs * BN;
   const int grid = (int)(items < num_sms() ? items : num_sms());
-  kern<<<grid, kThreads, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, p);
+  kern<<<grid, kThreads, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, p);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   return 0;
@@ -524,9 +585,9 @@ size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype) {
 }
 
 int sm100_tdp_fwd(const TdpArgs& a) {
-  // the two queries of a pair must fall in the same 64-row block
-  if (a.q_mod < 1 || a.q_mod > 32 || (a.q_mod & (a.q_mod - 1))) {
-    set_error("tensor-core path needs a power-of-two query shard count <= 32 (got %d)", a.q_mod);
+  // the two queries of a pair must fall in the same 128-row block
+  if (a.q_mod < 1 || a.q_mod > 64 || (a.q_mod & (a.q_mod - 1))) {
+    set_error("tensor-core path needs a power-of-two query shard count <= 64 (got %d)", a.q_mod);
     return -30;
   }
   if (a.dtype == TRITT_BF16) return a.D == 128 ? launch_fwd<128, __nv_bfloat16>(a) : launch_fwd<64, __nv_bfloat16>(a);
