@@ -46,6 +46,10 @@ namespace {
 using namespace sm100;
 
 constexpr int kBC = 128;  // key columns per slab
+#ifndef TRITT_EMU_BWD
+#define TRITT_EMU_BWD 0
+#endif
+constexpr int kEmuBwd = TRITT_EMU_BWD;  // every kEmuBwd-th exponential runs on the FMA pipe (0 = none)
 
 template <int D> struct BwdCfg {
   static constexpr int kTileA = 128 * D * 2;   // one 128-row operand / key / value tile
@@ -424,7 +428,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             if (cmax >= CW - 1) {
 #pragma unroll
               for (int i = 0; i < CW; i += 2)
-                pk[i >> 1] = pack2<T16>(exp2f(__uint_as_float(s[i]) - lse2), exp2f(__uint_as_float(s[i + 1]) - lse2));
+                pk[i >> 1] = pack2<T16>(exp2_mix<kEmuBwd>(__uint_as_float(s[i]) - lse2, i),
+                                        exp2_mix<kEmuBwd>(__uint_as_float(s[i + 1]) - lse2, i + 1));
             } else {
 #pragma unroll
               for (int i = 0; i < CW; i += 2) {

@@ -37,6 +37,10 @@ using namespace sm100;
 
 constexpr int kThreads = 512;
 constexpr int kBJ = 128;            // key columns per slab
+#ifndef TRITT_EMU_FWD
+#define TRITT_EMU_FWD 0
+#endif
+constexpr int kEmuFwd = TRITT_EMU_FWD;  // every kEmuFwd-th exponential runs on the FMA pipe (0 = none)
 constexpr float kRescaleGap = 8.f;  // rescale the accumulator only when the row max grew by more than 2^8
 
 template <int D> struct FwdCfg {
@@ -322,8 +326,17 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             tmem_wait_ld();
             const int cm = cmax - hf * 64;
             if (cm >= 63) {
+              // four independent chains instead of one 64-deep dependency
+              float m0 = __uint_as_float(sr[0]), m1 = __uint_as_float(sr[1]), m2 = __uint_as_float(sr[2]),
+                    m3 = __uint_as_float(sr[3]);
 #pragma unroll
-              for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+              for (int c = 4; c < 64; c += 4) {
+                m0 = fmaxf(m0, __uint_as_float(sr[c]));
+                m1 = fmaxf(m1, __uint_as_float(sr[c + 1]));
+                m2 = fmaxf(m2, __uint_as_float(sr[c + 2]));
+                m3 = fmaxf(m3, __uint_as_float(sr[c + 3]));
+              }
+              mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
             } else {
 #pragma unroll
               for (int c = 0; c < 64; ++c)
@@ -365,12 +378,16 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             const int cm = cmax - hf * 64;
             uint32_t pk[32];
             if (cm >= 63) {
+              float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
               for (int c = 0; c < 64; c += 2) {
-                const float p0 = exp2f(__uint_as_float(sr[c]) - m_used), p1 = exp2f(__uint_as_float(sr[c + 1]) - m_used);
-                psum += p0 + p1;
+                const float p0 = exp2_mix<kEmuFwd>(__uint_as_float(sr[c]) - m_used, c);
+                const float p1 = exp2_mix<kEmuFwd>(__uint_as_float(sr[c + 1]) - m_used, c + 1);
+                ps0 += p0;
+                ps1 += p1;
                 pk[c >> 1] = pack2<T16>(p0, p1);
               }
+              psum += ps0 + ps1;
             } else {
 #pragma unroll
               for (int c = 0; c < 64; c += 2) {
