@@ -32,6 +32,17 @@
 #include <type_traits>
 
 namespace tritt {
+#ifdef TRITT_TIMING
+// Development build only: per-CTA cycle counters of where each role waits.
+__device__ long long g_timing_fwd[148 * 16];
+#define FT_DECL long long tt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tt_t = clock64();
+#define FT(slot) { const long long tt_n = clock64(); tt_acc[slot] += tt_n - tt_t; tt_t = tt_n; }
+#define FT_FLUSH(basei) if (blockIdx.x < 148) { for (int i = 0; i < 8; ++i) g_timing_fwd[blockIdx.x * 16 + (basei) + i] = tt_acc[i]; }
+#else
+#define FT_DECL
+#define FT(slot)
+#define FT_FLUSH(basei)
+#endif
 namespace {
 using namespace sm100;
 
@@ -198,7 +209,13 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), 16384);  // row-major (MN-major) view
       uint32_t kt_count = 0, base = 0, n = 0;  // n: slabs finished so far (same for both tiles)
       bool alive = true;
-      auto wait_full = [&](uint32_t pos) { return mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag); };
+      FT_DECL
+      auto wait_full = [&](uint32_t pos) {
+        FT(0)
+        const bool ok = mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
+        FT(1)
+        return ok;
+      };
       auto release = [&](uint32_t pos) { mma_commit(&bars.ring_empty[pos % NS]); };
       // S_x = A_x * K1tile^T  (one chain of D/16 instructions)
       auto issue_s = [&](int x, uint32_t pos) {
@@ -224,7 +241,9 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         decode(item, bh, qa, qb);
         tile_counts(qa, qb, nkt, njt);
         for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
+          FT(0)
           if (!mbar_wait(&bars.a_ready, kt_count & 1, abort_flag)) { alive = false; break; }
+          FT(2)
           tc_fence_after();
           if (!wait_full(base)) { alive = false; break; }
           issue_s(0, base);
@@ -234,10 +253,13 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             const uint32_t pv = base + 2 * jt + 1, pk = base + 2 * jt + 2;
             const bool more = jt + 1 < njt;
             for (int x = 0; x < 2 && alive; ++x) {
+              FT(0)
               if (!mbar_wait(&bars.p_ready[x], n & 1, abort_flag)) { alive = false; break; }
+              FT(3)
               if (jt == 0) {
                 // the fold warpgroup must have drained the previous k-tile's accumulator of this tile
                 if (!mbar_wait(&bars.o_free[x], (kt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+                FT(4)
               }
               tc_fence_after();
               if (x == 0 && !wait_full(pv)) { alive = false; break; }
@@ -254,6 +276,8 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           base += 2 * njt;
         }
       }
+      FT(0)
+      FT_FLUSH(0)
     }
   } else if (warp >= 4 && warp < 12) {
     // ------------------------------------------------------------------ soft-max warpgroups
@@ -265,6 +289,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     float* stats = (float*)(smem + Cfg::kOffStats);
     uint32_t kt_count = 0, n = 0;
     bool alive = true;
+    FT_DECL
 
     for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
       int bh, qa, qb, nkt, njt;
@@ -275,7 +300,9 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 
       for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
         // ---- operand formation: A_a = s*Q[qa] (.) K2tile (in place), A_b = s*Q[qb] (.) K2tile
+        FT(0)
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.k2_full, kt_count & 1, abort_flag));
+        FT(1)
         if (!alive) break;
         {
           const int r = st & 127;
@@ -306,12 +333,15 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         }
         fence_async_smem();   // generic-proxy stores above -> visible to the tensor core's reads
         mbar_arrive(&bars.a_ready);
+        FT(2)
 
         // ---- walk over the slabs
         const uint32_t tS = tmem + lane_base + x * kBJ;
         float m_used = -INFINITY, l_sum = 0.f;
         for (int jt = 0; jt < njt; ++jt, ++n) {
+          FT(0)
           alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x], n & 1, abort_flag));
+          FT(3)
           if (!alive) break;
           tc_fence_after();
           if (jt == njt - 1) mbar_arrive(&bars.a_free);  // the last score product of this k-tile has read A_x
@@ -343,6 +373,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
                 if (c <= cm) mx = fmaxf(mx, __uint_as_float(sr[c]));
             }
           }
+          FT(4)
           if (jt == 0) {
             m_used = mx;  // nothing accumulated yet in this k-tile
           } else {
@@ -400,9 +431,11 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             tmem_st32(tS + hf * 32, pk);
           }
           l_sum += psum;
+          FT(5)
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(&bars.p_ready[x]);
+          FT(6)
         }
         if (!alive) break;
         // ---- hand this k-tile's row statistics to the fold warpgroup
@@ -415,6 +448,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       }
       if (!alive) break;
     }
+    if (x == 0 && row == 0) { FT_FLUSH(8) }
   } else if (warp >= 12) {
     // ------------------------------------------------------------------ fold warpgroup
     // After the last P*V of a k-tile: O[q_x,h] accumulates sum_r w_r acc_x[r,h] V2[k_r,h] with
@@ -585,6 +619,14 @@ int launch_fwd(const TdpArgs& a) {
 }
 
 }  // namespace
+
+#ifdef TRITT_TIMING
+}  // namespace tritt
+extern "C" int tritt_debug_read_timing_fwd(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, tritt::g_timing_fwd, sizeof(long long) * 148 * 16);
+}
+namespace tritt {
+#endif
 
 bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m) {
   if (op != TRITT_OP_TDP_FWD && op != TRITT_OP_TDP_BWD) return false;
