@@ -35,7 +35,6 @@
 // x <= q and, inside, the column slabs c <= q.
 #include "tritt_sm100_tdp.cuh"
 
-#include <cstdlib>
 #include <type_traits>
 
 namespace tritt {
@@ -87,7 +86,7 @@ struct BwdParams {
 struct BwdBarriers {
   uint64_t ring_full[4], ring_empty[4];
   uint64_t xy_full, a_ready, a_free;
-  uint64_t s_ready, dp_ready, p_ready, ds_ready;  // slab hand-offs
+  uint64_t s_ready, dp_ready, p_ready[2], ds_ready;  // slab hand-offs (P in two column halves)
   uint64_t gu_done, gu_free;                      // tile hand-offs with the fold warpgroup
   uint64_t sm_sync, fold_sync;
   uint64_t vec_free[2];                           // fold warpgroup -> soft-max: a copy of Q[q] / dO[q] is no longer read
@@ -138,7 +137,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     mbar_init(&bars.a_free, kNumSoftmax);
     mbar_init(&bars.s_ready, 1);
     mbar_init(&bars.dp_ready, 1);
-    mbar_init(&bars.p_ready, kNumSoftmax);
+    mbar_init(&bars.p_ready[0], kNumSoftmax);
+    mbar_init(&bars.p_ready[1], kNumSoftmax);
     mbar_init(&bars.ds_ready, kNumSoftmax);
     mbar_init(&bars.gu_done, 1);
     mbar_init(&bars.gu_free, 128);
@@ -274,14 +274,19 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       };
       // soft-max warpgroup g packed its CW columns of P into S[CW*g, CW*g + CW/2) and of dS into dP[CW*g, ...)
       constexpr int KPW = CW / 16;  // 16-deep MMA steps per warpgroup
-      auto issue_u = [&](uint32_t pos, uint32_t acc) {
+      // U is issued in two halves: the k-steps fed by the first half of every warpgroup's columns as soon as
+      // that half of P is there, the rest when the second half arrives (same accumulation chain).
+      auto issue_u_half = [&](uint32_t pos, uint32_t acc, int half) {
         const uint32_t st = pos % NS;
+        bool first = half == 0;
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
+          if (((k % KPW) >= KPW / 2) != (half == 1)) continue;
           const uint32_t a = tmem + Cfg::kTmemS + (k / KPW) * CW + (k % KPW) * 8;
-          mma_ts_lo(tmem + Cfg::kTmemU, a, ringMN + st * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
+          mma_ts_lo(tmem + Cfg::kTmemU, a, ringMN + st * kTile16 + k * (2048 >> 4), kHi, idesc_g, first ? acc : 1u);
+          first = false;
         }
-        mma_commit(&bars.ring_empty[st]);
+        if (half == 1) mma_commit(&bars.ring_empty[st]);
         TT(6)
       };
       auto issue_g = [&](uint32_t pos, uint32_t acc) {
@@ -308,14 +313,19 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           for (int c = 0; c < ncs && alive; ++c, ++n) {
             const bool more = c + 1 < ncs;
             TT(0)
-            if (!mbar_wait(&bars.p_ready, n & 1, abort_flag)) { alive = false; break; }
+            if (!mbar_wait(&bars.p_ready[0], n & 1, abort_flag)) { alive = false; break; }
             if (c == 0) {
               // the fold warpgroup must have drained the previous tile's G / U
               if (!mbar_wait(&bars.gu_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
             }
             TT(3)
             tc_fence_after();
-            issue_u(base + 2 * c + 1, c > 0);
+            issue_u_half(base + 2 * c + 1, c > 0, 0);
+            TT(0)
+            if (!mbar_wait(&bars.p_ready[1], n & 1, abort_flag)) { alive = false; break; }
+            TT(3)
+            tc_fence_after();
+            issue_u_half(base + 2 * c + 1, c > 0, 1);
             if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
             TT(0)
             if (!mbar_wait(&bars.ds_ready, n & 1, abort_flag)) { alive = false; break; }
@@ -419,31 +429,33 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           TT(3)
           if (!alive) break;
           tc_fence_after();
-          {
-            uint32_t s[CW];
+          static_assert(CW == 64, "the two-half hand-off of P is written for two soft-max warpgroups");
 #pragma unroll
-            for (int sc = 0; sc < CW / 32; ++sc) tmem_ld32(tS + sc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[sc * 32]));
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t s[32];
+            tmem_ld32(tS + hf * 32, s);
             tmem_wait_ld();
-            TT(4)
-            if (cmax >= CW - 1) {
+            const int cm = cmax - hf * 32;
+            if (cm >= 31) {
 #pragma unroll
-              for (int i = 0; i < CW; i += 2)
-                pk[i >> 1] = pack2<T16>(exp2_mix<kEmuBwd>(__uint_as_float(s[i]) - lse2, i),
-                                        exp2_mix<kEmuBwd>(__uint_as_float(s[i + 1]) - lse2, i + 1));
+              for (int i = 0; i < 32; i += 2)
+                pk[hf * 16 + (i >> 1)] = pack2<T16>(exp2_mix<kEmuBwd>(__uint_as_float(s[i]) - lse2, i),
+                                                    exp2_mix<kEmuBwd>(__uint_as_float(s[i + 1]) - lse2, i + 1));
             } else {
 #pragma unroll
-              for (int i = 0; i < CW; i += 2) {
-                const float p0 = i > cmax ? 0.f : exp2f(__uint_as_float(s[i]) - lse2);
-                const float p1 = i + 1 > cmax ? 0.f : exp2f(__uint_as_float(s[i + 1]) - lse2);
-                pk[i >> 1] = pack2<T16>(p0, p1);
+              for (int i = 0; i < 32; i += 2) {
+                const float p0 = i > cm ? 0.f : exp2f(__uint_as_float(s[i]) - lse2);
+                const float p1 = i + 1 > cm ? 0.f : exp2f(__uint_as_float(s[i + 1]) - lse2);
+                pk[hf * 16 + (i >> 1)] = pack2<T16>(p0, p1);
               }
             }
-            TT(5)
+            // P half -> S columns this thread has already read; hand it to the MMA warp right away
+            tmem_st16(tS + hf * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[hf * 16]));
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars.p_ready[hf]);
+            TT(4 + hf)
           }
-          tmem_st(tS, pk);  // P -> first half of this warpgroup's S columns (all of them already read)
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(&bars.p_ready);
           // ---- dP, P -> dS
           TT(2)
           alive = __all_sync(0xffffffffu, mbar_wait(&bars.dp_ready, n & 1, abort_flag));
@@ -635,20 +647,9 @@ int launch_bwd(const TdpArgs& a) {
   return simt_tdp_bwd_finalize(a.v1, a.dk1, a.dk2, a.dv1, a.dv2, n, a.dtype, part, a.stream);
 }
 
-// Soft-max warpgroups per CTA: 2 by default (measured faster: 103 ms against 120 ms at B=1, N=16, T=2048,
-// D=128); TRITT_BWD_WG=4 selects the 4-warpgroup build (tuning aid).
-int bwd_warpgroups() {
-  static int v = 0;
-  if (!v) {
-    const char* e = getenv("TRITT_BWD_WG");
-    v = (e && atoi(e) == 4) ? 4 : 2;
-  }
-  return v;
-}
-
 template <int D, typename T16>
 int launch_bwd_any(const TdpArgs& a) {
-  return bwd_warpgroups() == 2 ? launch_bwd<D, T16, 2>(a) : launch_bwd<D, T16, 4>(a);
+  return launch_bwd<D, T16, 2>(a);
 }
 
 }  // namespace
