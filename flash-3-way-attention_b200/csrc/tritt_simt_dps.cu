@@ -301,6 +301,24 @@ int pick_threads(int nvec, int D) {
   return nt;
 }
 
+#include "tritt_simt_dps_quad.cuh"
+
+enum { ATTN_FWD = 0, ATTN_BWD_ROW = 1, ATTN_BWD_COL = 2 };
+
+// Register-resident kernels for head dimensions 16..128 (a quad of lanes per owner).
+template <typename T, int DQ>
+int launch_quad(int kind, const AttnParams& p, int BN, cudaStream_t stream) {
+  const dim3 grid((p.T + kQuadOwners - 1) / kQuadOwners, BN);
+  switch (kind) {
+    case ATTN_FWD: attn_fwd_quad<T, DQ><<<grid, 128, 0, stream>>>(p); break;
+    case ATTN_BWD_ROW: attn_bwd_row_quad<T, DQ><<<grid, 128, 0, stream>>>(p); break;
+    default: attn_bwd_col_quad<T, DQ><<<grid, 128, 0, stream>>>(p); break;
+  }
+  count_launch();
+  TRITT_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 template <typename K>
 int launch_attn(K kern, const AttnParams& p, int nvec, int ntiles, int BN, cudaStream_t stream) {
   const int nt = pick_threads(nvec, p.D);
@@ -314,6 +332,21 @@ int launch_attn(K kern, const AttnParams& p, int nvec, int ntiles, int BN, cudaS
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+// Picks the register-resident kernels when the head dimension allows, else the shared-memory ones.
+template <typename T>
+int run_attn(int kind, const AttnParams& p, int BN, cudaStream_t stream) {
+  switch (p.D) {
+    case 16: return launch_quad<T, 4>(kind, p, BN, stream);
+    case 32: return launch_quad<T, 8>(kind, p, BN, stream);
+    case 64: return launch_quad<T, 16>(kind, p, BN, stream);
+    case 128: return launch_quad<T, 32>(kind, p, BN, stream);
+    default: break;
+  }
+  if (kind == ATTN_FWD) return launch_attn(attn_fwd_kernel<T>, p, 2, 2, BN, stream);
+  if (kind == ATTN_BWD_ROW) return launch_attn(attn_bwd_row_kernel<T>, p, 3, 2, BN, stream);
+  return launch_attn(attn_bwd_col_kernel<T>, p, 4, 3, BN, stream);
 }
 
 // workspace layout (floats): Y [n] | LSEin [r] | then, backward only:
@@ -345,7 +378,7 @@ int dps_inner_fwd(const DpsArgs& a, const DpsWs& w) {
   p.out_f32 = w.Y;
   p.out_lse = w.lse_in;
   p.T = a.T; p.D = a.D; p.causal = a.causal; p.win = a.k_diff; p.alpha = a.alpha;
-  return launch_attn(attn_fwd_kernel<T>, p, 2, 2, a.B * a.N, a.stream);
+  return run_attn<T>(ATTN_FWD, p, a.B * a.N, a.stream);
 }
 
 template <typename T>
@@ -362,7 +395,7 @@ int dps_fwd_t(const DpsArgs& a) {
   p.out_t = a.out_o;
   p.out_lse = a.out_m;
   p.T = a.T; p.D = a.D; p.causal = a.causal; p.win = a.T; p.alpha = a.alpha;
-  return launch_attn(attn_fwd_kernel<T>, p, 2, 2, a.B * a.N, a.stream);
+  return run_attn<T>(ATTN_FWD, p, a.B * a.N, a.stream);
 }
 
 template <typename T>
@@ -388,13 +421,13 @@ int dps_bwd_t(const DpsArgs& a) {
   p.T = a.T; p.D = a.D; p.causal = a.causal; p.win = a.T; p.alpha = a.alpha;
   AttnParams pr = p;
   pr.d_rows_t = a.dq;
-  rc = launch_attn(attn_bwd_row_kernel<T>, pr, 3, 2, BN, a.stream);
+  rc = run_attn<T>(ATTN_BWD_ROW, pr, BN, a.stream);
   if (rc) return rc;
   AttnParams pc = p;
   pc.d_kc_f32 = w.dK2a;
   pc.d_vc_f32 = w.dW;
   pc.gsum = w.g;
-  rc = launch_attn(attn_bwd_col_kernel<T>, pc, 4, 3, BN, a.stream);
+  rc = run_attn<T>(ATTN_BWD_COL, pc, BN, a.stream);
   if (rc) return rc;
   dps_mid_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>(w.dW, w.Y, (const T*)a.v2, w.g, (T*)a.dv2, w.dY,
                                                                         w.Dt, r, a.D);
@@ -413,12 +446,12 @@ int dps_bwd_t(const DpsArgs& a) {
   qr.d_rows_f32 = w.dK2a;  // dK2 = (as outer key) + (as inner query)
   qr.d_rows_t = a.dk2;
   qr.d_rows_accumulate = 1;
-  rc = launch_attn(attn_bwd_row_kernel<T>, qr, 3, 2, BN, a.stream);
+  rc = run_attn<T>(ATTN_BWD_ROW, qr, BN, a.stream);
   if (rc) return rc;
   AttnParams qc = q;
   qc.d_kc_t = a.dk1;
   qc.d_vc_f32 = w.dsV1;
-  rc = launch_attn(attn_bwd_col_kernel<T>, qc, 4, 3, BN, a.stream);
+  rc = run_attn<T>(ATTN_BWD_COL, qc, BN, a.stream);
   if (rc) return rc;
   dps_dv1_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, a.stream>>>(w.dsV1, (const T*)a.v1, (T*)a.dv1, n);
   count_launch();

@@ -108,3 +108,10 @@ def test_16bit_inputs(dtype, tol):
     assert (out.float() - z_ref).abs().max() <= tol
     for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), grads, g_ref):
         assert (a.float() - b).abs().max() <= tol * max(1.0, float(b.abs().max())), name
+
+
+@pytest.mark.parametrize("D", [8, 16, 128, 256])
+def test_other_head_dims(D):
+    """Head dimensions on both kernel families: 16..128 run the register-resident kernels, the rest the
+    shared-memory ones."""
+    run_and_compare(seq_len=40, causal=True, k_diff=40, B=1, N=2, D=D, seed=D)
