@@ -45,7 +45,9 @@ __device__ __forceinline__ float exp2_fma(float x) {
 // warps are bound by issue slots and latency, not by the special-function unit, so the default is 0.
 template <int EMU>
 __device__ __forceinline__ float exp2_mix(float x, int idx) {
-  if (EMU > 0 && (idx % EMU) == EMU - 1) return exp2_fma(x);
+  if constexpr (EMU > 0) {
+    if ((idx % EMU) == EMU - 1) return exp2_fma(x);
+  }
   return exp2f(x);
 }
 

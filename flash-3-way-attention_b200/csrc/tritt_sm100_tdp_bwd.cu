@@ -87,7 +87,7 @@ struct BwdBarriers {
   uint64_t ring_full[4], ring_empty[4];
   uint64_t xy_full, a_ready, a_free;
   uint64_t s_ready, dp_ready, p_ready[2], ds_ready;  // slab hand-offs (P in two column halves)
-  uint64_t gu_done, gu_free;                      // tile hand-offs with the fold warpgroup
+  uint64_t gu_done, u_free, g_free;               // tile hand-offs with the fold warpgroup (U is drained first)
   uint64_t sm_sync, fold_sync;
   uint64_t vec_free[2];                           // fold warpgroup -> soft-max: a copy of Q[q] / dO[q] is no longer read
   uint32_t tmem_base;
@@ -141,7 +141,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     mbar_init(&bars.p_ready[1], kNumSoftmax);
     mbar_init(&bars.ds_ready, kNumSoftmax);
     mbar_init(&bars.gu_done, 1);
-    mbar_init(&bars.gu_free, 128);
+    mbar_init(&bars.u_free, 128);
+    mbar_init(&bars.g_free, 128);
     mbar_init(&bars.sm_sync, kNumSoftmax);
     mbar_init(&bars.fold_sync, 128);
     mbar_init(&bars.vec_free[0], 128);
@@ -315,8 +316,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             TT(0)
             if (!mbar_wait(&bars.p_ready[0], n & 1, abort_flag)) { alive = false; break; }
             if (c == 0) {
-              // the fold warpgroup must have drained the previous tile's G / U
-              if (!mbar_wait(&bars.gu_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+              // the fold warpgroup must have drained the previous tile's U
+              if (!mbar_wait(&bars.u_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
             }
             TT(3)
             tc_fence_after();
@@ -329,6 +330,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
             TT(0)
             if (!mbar_wait(&bars.ds_ready, n & 1, abort_flag)) { alive = false; break; }
+            if (c == 0) {
+              // ... and the previous tile's G
+              if (!mbar_wait(&bars.g_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+            }
             TT(3)
             tc_fence_after();
             issue_g(base + 2 * c, c > 0);
@@ -524,13 +529,14 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
         const int x_r = xt * 128 + row;
         const bool x_ok = (p.causal ? (x_r <= q) : true) && x_r < T;
+        const bool warp_rows_live = xt * 128 + wq * 32 <= (p.causal ? q : T - 1);
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.gu_done, xt_count & 1, abort_flag));
         if (!alive) break;
         tc_fence_after();
 #pragma unroll 1
         for (int pc = 0; pc < 2 * (D / 32); ++pc, ++round) {
-          const bool is_u = pc >= D / 32;
-          const int h0 = (is_u ? pc - D / 32 : pc) * 32;
+          const bool is_u = pc < D / 32;   // U first: the next tile needs its accumulator earlier than G's
+          const int h0 = (is_u ? pc : pc - D / 32) * 32;
           // role 0, G pieces: this row's X values for the dQ product (issued early to hide the latency)
           uint4 xr[4];
           const bool want_dq = !is_u && role == 0;
@@ -547,15 +553,26 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           // later query and overwrite an older copy of these vectors
           float v[32];
           {
-            const float* mul = is_u ? dov : qv;
+            const float4* mul = reinterpret_cast<const float4*>((is_u ? dov : qv) + h0);
             const float sc = is_u ? 1.f : p.alpha;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = sc * __uint_as_float(g[i]) * mul[h0 + i];
+            for (int i4 = 0; i4 < 8; ++i4) {
+              const float4 m = mul[i4];
+              v[i4 * 4] = sc * __uint_as_float(g[i4 * 4]) * m.x;
+              v[i4 * 4 + 1] = sc * __uint_as_float(g[i4 * 4 + 1]) * m.y;
+              v[i4 * 4 + 2] = sc * __uint_as_float(g[i4 * 4 + 2]) * m.z;
+              v[i4 * 4 + 3] = sc * __uint_as_float(g[i4 * 4 + 3]) * m.w;
+            }
+          }
+          if (pc == D / 32 - 1) {
+            // last piece of U is in registers: that accumulator may be overwritten
+            tc_fence_before();
+            mbar_arrive(&bars.u_free);
           }
           if (pc == 2 * (D / 32) - 1) {
-            // last piece of this tile is in registers: the accumulators may be overwritten
+            // likewise G
             tc_fence_before();
-            mbar_arrive(&bars.gu_free);
+            mbar_arrive(&bars.g_free);
             if (xt == nxt - 1) mbar_arrive(&bars.vec_free[item_count & 1]);  // and this query's vectors are done with
           }
           uint8_t* slot = slots + (round & 1) * 4096;
@@ -568,7 +585,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
                 make_float4(v[i4 * 4], v[i4 * 4 + 1], v[i4 * 4 + 2], v[i4 * 4 + 3]);
           fence_async_smem();
           __syncwarp();
-          if (lane == 0) {
+          // (rows beyond the query carry zeros: a warp whose 32 rows are all beyond it has nothing to add)
+          if (lane == 0 && warp_rows_live) {
             tma_reduce_add_3d(is_u ? tmDY : tmDX, slot, h0, xt * 128 + wq * 32, bh);
             bulk_commit();
           }
