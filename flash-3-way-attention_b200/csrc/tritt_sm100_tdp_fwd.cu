@@ -73,6 +73,7 @@ struct FwdParams {
   float* lse;
   const void *q, *v2;
   int T, BN, nq, q_mod, q_rem, causal, n_pairs;
+  int k1w, k2w, kkl, kkr;  // windows of the causal mask (T or more = unbounded)
   float scale2;  // alpha * log2(e)
   int* status;
 };
@@ -144,10 +145,30 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     qa = p.q_rem + ia * p.q_mod;
     qb = p.q_rem + ib * p.q_mod;
   };
-  auto tile_counts = [&](int qa, int qb, int& nkt, int& njt) {
-    const int qmax = max(qa, qb);
-    nkt = p.causal ? qmax / 128 + 1 : (T + 127) / 128;
-    njt = p.causal ? qmax / kBJ + 1 : (T + kBJ - 1) / kBJ;
+  // Tiles a query pair visits (qa <= qb).  Causal mask: j <= q <= j + k1w, k <= q <= k + k2w, k - kkl <= j <= k + kkr.
+  // k-tiles: rows k in [max(0, qa - k2w, qa - k1w - kkr), qb]  (rows below the third bound see no column at all);
+  // slabs of k-tile kt: columns j in [max(0, qa - k1w, k_first - kkl), min(qb, k_last + kkr)], never empty.
+  auto k_range = [&](int qa, int qb, int& kt0, int& nkt) {
+    if (!p.causal) {
+      kt0 = 0;
+      nkt = (T + 127) / 128;
+      return;
+    }
+    const int klo = max(0, max(qa - p.k2w, qa - p.k1w - p.kkr));
+    kt0 = klo / 128;
+    nkt = qb / 128 - kt0 + 1;
+  };
+  auto j_range = [&](int qa, int qb, int kt, int& jt0, int& njt) {
+    if (!p.causal) {
+      jt0 = 0;
+      njt = (T + kBJ - 1) / kBJ;
+      return;
+    }
+    const int klo = max(0, max(qa - p.k2w, qa - p.k1w - p.kkr));
+    const int ka = max(kt * 128, klo), kb = min(kt * 128 + 127, qb);
+    const int ja = max(0, max(qa - p.k1w, ka - p.kkl)), jb = min(qb, kb + p.kkr);
+    jt0 = ja / kBJ;
+    njt = jb / kBJ - jt0 + 1;
   };
 
   if (warp == 0) {
@@ -168,20 +189,22 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         return true;
       };
       for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-        int bh, qa, qb, nkt, njt;
+        int bh, qa, qb, kt0, nkt;
         decode(item, bh, qa, qb);
-        tile_counts(qa, qb, nkt, njt);
-        for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
+        k_range(qa, qb, kt0, nkt);
+        for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
+          int jt0, njt;
+          j_range(qa, qb, kt, jt0, njt);
           // the first K1 tile does not depend on the previous k-tile: fetch it before waiting for the operand buffer
-          alive = load_stage(&tmK1, 0, bh);
+          alive = load_stage(&tmK1, jt0 * kBJ, bh);
           if (!alive || !mbar_wait(&bars.a_free, (kt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
           mbar_arrive_expect_tx(&bars.k2_full, Cfg::kTileA);
           for (int hh = 0; hh < KH; ++hh)
             tma_load_3d(smem + Cfg::kOffAa + hh * 16384, &tmK2, &bars.k2_full, hh * 64, kt * 128, bh);
           // ring order: K1(0), V(0), K1(1), V(1), ...
-          for (int jt = 0; jt < njt && alive; ++jt) {
+          for (int jt = jt0; jt < jt0 + njt && alive; ++jt) {
             alive = load_stage(&tmSV1, jt * kBJ, bh);
-            if (alive && jt + 1 < njt) alive = load_stage(&tmK1, (jt + 1) * kBJ, bh);
+            if (alive && jt + 1 < jt0 + njt) alive = load_stage(&tmK1, (jt + 1) * kBJ, bh);
           }
         }
       }
@@ -237,10 +260,12 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       };
 
       for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-        int bh, qa, qb, nkt, njt;
+        int bh, qa, qb, kt0, nkt;
         decode(item, bh, qa, qb);
-        tile_counts(qa, qb, nkt, njt);
-        for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
+        k_range(qa, qb, kt0, nkt);
+        for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
+          int jt0, njt;
+          j_range(qa, qb, kt, jt0, njt);
           FT(0)
           if (!mbar_wait(&bars.a_ready, kt_count & 1, abort_flag)) { alive = false; break; }
           FT(2)
@@ -292,13 +317,25 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     FT_DECL
 
     for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-      int bh, qa, qb, nkt, njt;
+      int bh, qa, qb, kt0, nkt;
       decode(item, bh, qa, qb);
-      tile_counts(qa, qb, nkt, njt);
+      k_range(qa, qb, kt0, nkt);
       const int qx = x == 0 ? qa : qb;
       const T16* Qg = (const T16*)p.q + (size_t)bh * T * D;
 
-      for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
+      for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
+        int jt0, njt;
+        j_range(qa, qb, kt, jt0, njt);
+        // Columns this row may see: [c_lo, c_hi].  A row outside the k range of its query (its weight in the
+        // fold is zero) keeps the query's own column range so that it never sees an empty one by construction;
+        // a row inside can still see none in a slab, or at all: its maximum then stays -inf and its P zero.
+        int c_lo = 0, c_hi = T - 1;
+        if (p.causal) {
+          const int k_r = kt * 128 + row;
+          const bool in_k = k_r <= qx && qx - k_r <= p.k2w;
+          c_lo = max(qx - p.k1w, in_k ? k_r - p.kkl : 0);
+          c_hi = in_k ? min(qx, k_r + p.kkr) : qx;
+        }
         // ---- operand formation: A_a = s*Q[qa] (.) K2tile (in place), A_b = s*Q[qb] (.) K2tile
         FT(0)
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.k2_full, kt_count & 1, abort_flag));
@@ -345,8 +382,11 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           if (!alive) break;
           tc_fence_after();
           if (jt == njt - 1) mbar_arrive(&bars.a_free);  // the last score product of this k-tile has read A_x
-          // column bound: j <= q (causal) / j < T
-          const int cmax = (p.causal ? qx : T - 1) - jt * kBJ;
+          // this row's valid columns within the slab: [lo, hi]; the warp takes the unmasked path when every
+          // row sees the whole slab
+          const int j0 = (jt0 + jt) * kBJ;
+          const int lo = c_lo - j0, hi = c_hi - j0;
+          const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= kBJ - 1);
           // pass 1: row maximum
           float mx = -INFINITY;
 #pragma unroll
@@ -354,8 +394,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             uint32_t sr[64];
             tmem_ld64(tS + hf * 64, sr);
             tmem_wait_ld();
-            const int cm = cmax - hf * 64;
-            if (cm >= 63) {
+            if (full) {
               // four independent chains instead of one 64-deep dependency
               float m0 = __uint_as_float(sr[0]), m1 = __uint_as_float(sr[1]), m2 = __uint_as_float(sr[2]),
                     m3 = __uint_as_float(sr[3]);
@@ -368,9 +407,10 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
               }
               mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
             } else {
+              const int l2 = lo - hf * 64, h2 = hi - hf * 64;
 #pragma unroll
               for (int c = 0; c < 64; ++c)
-                if (c <= cm) mx = fmaxf(mx, __uint_as_float(sr[c]));
+                if (c >= l2 && c <= h2) mx = fmaxf(mx, __uint_as_float(sr[c]));
             }
           }
           FT(4)
@@ -406,9 +446,8 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             uint32_t sr[64];
             tmem_ld64(tS + hf * 64, sr);
             tmem_wait_ld();
-            const int cm = cmax - hf * 64;
             uint32_t pk[32];
-            if (cm >= 63) {
+            if (full) {
               float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
               for (int c = 0; c < 64; c += 2) {
@@ -420,10 +459,12 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
               }
               psum += ps0 + ps1;
             } else {
+              // (a row with no valid column so far has m_used = -inf and selects 0 everywhere)
+              const int l2 = lo - hf * 64, h2 = hi - hf * 64;
 #pragma unroll
               for (int c = 0; c < 64; c += 2) {
-                const float p0 = c <= cm ? exp2f(__uint_as_float(sr[c]) - m_used) : 0.f;
-                const float p1 = c + 1 <= cm ? exp2f(__uint_as_float(sr[c + 1]) - m_used) : 0.f;
+                const float p0 = (c >= l2 && c <= h2) ? exp2f(__uint_as_float(sr[c]) - m_used) : 0.f;
+                const float p1 = (c + 1 >= l2 && c + 1 <= h2) ? exp2f(__uint_as_float(sr[c + 1]) - m_used) : 0.f;
                 psum += p0 + p1;
                 pk[c >> 1] = pack2<T16>(p0, p1);
               }
@@ -468,13 +509,13 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       return __all_sync(0xffffffffu, ok);
     };
     for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-      int bh, qa, qb, nkt, njt;
+      int bh, qa, qb, kt0, nkt;
       decode(item, bh, qa, qb);
-      tile_counts(qa, qb, nkt, njt);
+      k_range(qa, qb, kt0, nkt);
       const T16* V2g = (const T16*)p.v2 + (size_t)bh * T * D;
       // running state per tile; thread `row` (< D) owns output column h = row
       float M_run[2] = {-INFINITY, -INFINITY}, L_run[2] = {0.f, 0.f}, O_run[2] = {0.f, 0.f};
-      for (int kt = 0; kt < nkt && alive; ++kt, ++kt_count) {
+      for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
         const int k_r = kt * 128 + row;
         const uint32_t par = kt_count & 1;
         // row statistics of both tiles
@@ -488,7 +529,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           m_r[x] = srow[0];
           l_r[x] = srow[1];
           const int qx = x == 0 ? qa : qb;
-          valid[x] = p.causal ? (k_r <= qx) : (k_r < T);
+          valid[x] = p.causal ? (k_r <= qx && qx - k_r <= p.k2w) : (k_r < T);
           float wm = valid[x] ? m_r[x] : -INFINITY;
 #pragma unroll
           for (int o = 16; o >= 1; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
@@ -499,9 +540,10 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         float Mt[2], w[2];
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-          // finite: row k0 of the tile is always valid
+          // -inf when no row of this tile saw a valid column for this query (possible under narrow windows): the
+          // tile then contributes nothing; a single such row has m_r = -inf and gets weight 0
           Mt[x] = fmaxf(fmaxf(fstat[x * 8], fstat[x * 8 + 1]), fmaxf(fstat[x * 8 + 2], fstat[x * 8 + 3]));
-          w[x] = valid[x] ? exp2f(m_r[x] - Mt[x]) : 0.f;
+          w[x] = (valid[x] && m_r[x] > -INFINITY) ? exp2f(m_r[x] - Mt[x]) : 0.f;
           float lw = w[x] * l_r[x];
 #pragma unroll
           for (int o = 16; o >= 1; o >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, o);
@@ -548,6 +590,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         if (!fold_sync()) { alive = false; break; }
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
+          if (!(Mt[x] > -INFINITY)) continue;   // nothing valid in this tile for this query
           const float Lt = fstat[x * 8 + 4] + fstat[x * 8 + 5] + fstat[x * 8 + 6] + fstat[x * 8 + 7];
           const float Mn = fmaxf(M_run[x], Mt[x]);
           const float ca = exp2f(M_run[x] - Mn), cb = exp2f(Mt[x] - Mn);
@@ -605,6 +648,10 @@ int launch_fwd(const TdpArgs& a) {
   p.nq = a.q_rem < a.T ? (a.T - a.q_rem + a.q_mod - 1) / a.q_mod : 0;
   p.n_pairs = (p.nq + 1) / 2;
   p.causal = a.mask.causal;
+  p.k1w = a.mask.k1w;
+  p.k2w = a.mask.k2w;
+  p.kkl = a.mask.kkl;
+  p.kkr = a.mask.kkr;
   p.scale2 = a.alpha * kLog2e;
   p.status = a.status_word;
   if (p.nq == 0) return 0;
@@ -632,7 +679,8 @@ bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m) {
   if (op != TRITT_OP_TDP_FWD && op != TRITT_OP_TDP_BWD) return false;
   if (dtype != TRITT_BF16 && dtype != TRITT_F16) return false;
   if (D != 64 && D != 128) return false;
-  if (!m.full_windows()) return false;
+  // the forward handles every window of the causal mask; the backward the unbounded ones
+  if (op == TRITT_OP_TDP_BWD && !m.full_windows()) return false;
   return T >= 1;
 }
 

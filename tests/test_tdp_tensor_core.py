@@ -151,3 +151,51 @@ def test_backward_query_shards_sum_to_full_gradient():
     assert _native.read_status(torch.device(DEV)) == 0
     for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), [dq] + outs, full):
         assert float((a.float() - b.float()).abs().max()) <= 2e-2 * max(1.0, float(b.float().abs().max())), name
+
+
+WINDOWS = [
+    (8, 8, 4, 4),          # the reference tests' narrow band (tests/test_triple_dot_product.py)
+    (128, 128, 32, 32),    # the reference's banded forward benchmark (b200/bench_b200.py)
+    (300, 100, 50, 20),
+    (100, 300, 20, 50),
+    (10, 1000, 3, 5),      # k2 window far wider than k1 window + band: rows that see no column at all
+    (1000, 10, 300, 0),
+    (1, 1, 1, 1),          # the entry point's defaults
+    (0, 0, 0, 0),          # only j = k = q
+    (200, 200, 0, 200),
+]
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("windows", WINDOWS)
+def test_forward_windows_match_oracle(windows, D):
+    """Causal mask with k1 / k2 windows and the (j, k) band on the tensor-core forward."""
+    B, N, T, dtype = 1, 2, 333, torch.bfloat16
+    q, k1, k2, v1, v2, _ = orc.make_inputs(B, N, T, D, scale=0.5, seed=11 + D, dtype=dtype)
+    code = _native.dtype_code(dtype)
+    assert _native.tdp_path(_native.OP_TDP_FWD, T, D, code, True, *windows) == _native.PATH_TCGEN05
+    dq, dk1, dk2, dv1, dv2 = (t.to(DEV) for t in (q, k1, k2, v1, v2))
+    o = torch.empty_like(dq)
+    lse = torch.empty(B, N, T, device=DEV)
+    _native.tdp_fwd(dq, dk1, dk2, dv1, dv2, o, lse, 1.0 / D, True, *windows)
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0, "a bounded barrier wait ran out"
+    z_ref, lse_ref = orc.tdp_forward(*(t.float() for t in (q, k1, k2, v1, v2)), 1.0 / D, True, *windows)
+    assert torch.isfinite(o.float()).all() and torch.isfinite(lse).all()
+    assert float((o.float().cpu() - z_ref).abs().max()) <= TOL[dtype]
+    assert float((lse.cpu() - lse_ref).abs().max()) <= 2e-2
+
+
+def test_forward_windows_large_logits_fp16():
+    """Unit-variance inputs with alpha = 1/8 under a narrow band: rows whose first slab is empty and a moving maximum."""
+    B, N, T, D, dtype = 1, 2, 400, 64, torch.float16
+    windows = (150, 90, 40, 10)
+    q, k1, k2, v1, v2, _ = orc.make_inputs(B, N, T, D, scale=1.0, seed=23, dtype=dtype)
+    dq, dk1, dk2, dv1, dv2 = (t.to(DEV) for t in (q, k1, k2, v1, v2))
+    o = torch.empty_like(dq)
+    lse = torch.empty(B, N, T, device=DEV)
+    _native.tdp_fwd(dq, dk1, dk2, dv1, dv2, o, lse, 1 / 8, True, *windows)
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0
+    z_ref, _ = orc.tdp_forward(*(t.float() for t in (q, k1, k2, v1, v2)), 1 / 8, True, *windows)
+    assert float((o.float().cpu() - z_ref).abs().max()) <= 1e-2
