@@ -79,6 +79,7 @@ struct BwdParams {
   const float* lse;
   void* dq;
   int T, BN, nq, q_mod, q_rem, causal;
+  int k1w, k2w, kkl, kkr;  // windows of the causal mask (T or more = unbounded)
   float alpha;
   int* status;
 };
@@ -169,9 +170,35 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     bh = (int)(r % p.BN);
     q = p.q_rem + (p.nq - 1 - (int)(r / p.BN)) * p.q_mod;
   };
-  auto tile_counts = [&](int q, int& nxt, int& ncs) {
-    nxt = p.causal ? q / 128 + 1 : (T + 127) / 128;
-    ncs = p.causal ? q / kBC + 1 : (T + kBC - 1) / kBC;
+  // Causal mask j <= q <= j + k1w, k <= q <= k + k2w, k - kkl <= j <= k + kkr, seen from a role's rows x and
+  // columns c (role 0: x = k, c = j; role 1: x = j, c = k):  x in [q - xw, q],  c in [q - cw, q],  c in [x - below, x + above].
+  struct Win { int xw, cw, below, above; };
+  auto role_win = [&](int role) {
+    return role == 0 ? Win{p.k2w, p.k1w, p.kkl, p.kkr} : Win{p.k1w, p.k2w, p.kkr, p.kkl};
+  };
+  // row tiles of a query: rows [max(0, q - xw, q - cw - above), q]  (rows below the third bound see no column);
+  // column slabs of row tile xt: [max(0, q - cw, x_first - below), min(q, x_last + above)], never empty
+  auto x_range = [&](int q, const Win& w, int& xt0, int& nxt) {
+    if (!p.causal) {
+      xt0 = 0;
+      nxt = (T + 127) / 128;
+      return;
+    }
+    const int xlo = max(0, max(q - w.xw, q - w.cw - w.above));
+    xt0 = xlo / 128;
+    nxt = q / 128 - xt0 + 1;
+  };
+  auto c_range = [&](int q, const Win& w, int xt, int& c0, int& ncs) {
+    if (!p.causal) {
+      c0 = 0;
+      ncs = (T + kBC - 1) / kBC;
+      return;
+    }
+    const int xlo = max(0, max(q - w.xw, q - w.cw - w.above));
+    const int xa = max(xt * 128, xlo), xb = min(xt * 128 + 127, q);
+    const int ca = max(0, max(q - w.cw, xa - w.below)), cb = min(q, xb + w.above);
+    c0 = ca / kBC;
+    ncs = cb / kBC - c0 + 1;
   };
 
   if (warp == 0) {
@@ -196,22 +223,25 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         return true;
       };
       for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-        int role, bh, q, nxt, ncs;
+        int role, bh, q, xt0, nxt;
         decode(item, role, bh, q);
-        tile_counts(q, nxt, ncs);
+        const Win win = role_win(role);
+        x_range(q, win, xt0, nxt);
         // role 0: columns K1 / SiLU(V1), rows K2 / V2;   role 1: columns K2 / V2, rows K1 / SiLU(V1)
         const CUtensorMap* tmKc = role == 0 ? &tmK1 : &tmK2;
         const CUtensorMap* tmVc = role == 0 ? &tmSV1 : &tmV2;
         const CUtensorMap* tmX = role == 0 ? &tmK2 : &tmK1;
         const CUtensorMap* tmY = role == 0 ? &tmV2 : &tmSV1;
-        for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
+        for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
+          int c0, ncs;
+          c_range(q, win, xt, c0, ncs);
           if (!mbar_wait(&bars.a_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
           mbar_arrive_expect_tx(&bars.xy_full, 2 * Cfg::kTileA);
           for (int hh = 0; hh < KH; ++hh) {
             tma_load_3d(smem + Cfg::kOffA + hh * 16384, tmX, &bars.xy_full, hh * 64, xt * 128, bh);
             tma_load_3d(smem + Cfg::kOffA2 + hh * 16384, tmY, &bars.xy_full, hh * 64, xt * 128, bh);
           }
-          for (int c = 0; c < ncs && alive; ++c) {
+          for (int c = c0; c < c0 + ncs && alive; ++c) {
             alive = load_stage(tmKc, c * kBC, bh);
             if (alive) alive = load_stage(tmVc, c * kBC, bh);
           }
@@ -302,10 +332,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       };
 
       for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-        int role, bh, q, nxt, ncs;
+        int role, bh, q, xt0, nxt;
         decode(item, role, bh, q);
-        tile_counts(q, nxt, ncs);
-        for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
+        const Win win = role_win(role);
+        x_range(q, win, xt0, nxt);
+        for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
+          int c0, ncs;
+          c_range(q, win, xt, c0, ncs);
           TT(0)
           if (!mbar_wait(&bars.a_ready, xt_count & 1, abort_flag)) { alive = false; break; }
           TT(2)
@@ -365,9 +398,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     };
 
     for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++item_count) {
-      int role, bh, q, nxt, ncs;
+      int role, bh, q, xt0, nxt;
       decode(item, role, bh, q);
-      tile_counts(q, nxt, ncs);
+      const Win win = role_win(role);
+      x_range(q, win, xt0, nxt);
       const size_t hb = (size_t)bh * T * D;
       float* qv = vec + (item_count & 1) * 2 * D;  // Q[q, :] (double-buffered by item: the fold warpgroup of the
       float* dov = qv + D;                         // dO[q, :]  previous item may still be reading its copy)
@@ -394,7 +428,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e;
       const float scale2 = p.alpha * kLog2e;
 
-      for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
+      for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
+        int c0, ncs;
+        c_range(q, win, xt, c0, ncs);
         // ---- operand formation (in place): A = scale2*Q[q] (.) X tile,  A' = dO[q] (.) Y tile
         TT(0)
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.xy_full, xt_count & 1, abort_flag));
@@ -420,13 +456,19 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         fence_async_smem();
         mbar_arrive(&bars.a_ready);
 
+        // columns this row sees: [c_lo, c_hi] (empty for a row outside its own range: its P is zero)
         const int x_r = xt * 128 + row;
-        const bool row_valid = p.causal ? (x_r <= q) : (x_r < T);
+        int c_lo = 0, c_hi = x_r < T ? T - 1 : -1;
+        if (p.causal) {
+          const bool row_valid = x_r <= q && q - x_r <= win.xw;
+          c_lo = max(q - win.cw, x_r - win.below);
+          c_hi = row_valid ? min(q, x_r + win.above) : c_lo - 1;
+        }
         const uint32_t tS = tmem + lane_base + Cfg::kTmemS + wg * CW;
         const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + wg * CW;
 
         for (int c = 0; c < ncs; ++c, ++n) {
-          const int cmax = (row_valid ? (p.causal ? q : T - 1) - c * kBC : -1) - wg * CW;
+          const int lo = c_lo - (c0 + c) * kBC - wg * CW, hi = c_hi - (c0 + c) * kBC - wg * CW;
           uint32_t pk[CW / 2];
           // ---- S -> P
           TT(2)
@@ -440,8 +482,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             uint32_t s[32];
             tmem_ld32(tS + hf * 32, s);
             tmem_wait_ld();
-            const int cm = cmax - hf * 32;
-            if (cm >= 31) {
+            const int l2 = lo - hf * 32, h2 = hi - hf * 32;
+            if (l2 <= 0 && h2 >= 31) {
 #pragma unroll
               for (int i = 0; i < 32; i += 2)
                 pk[hf * 16 + (i >> 1)] = pack2<T16>(exp2_mix<kEmuBwd>(__uint_as_float(s[i]) - lse2, i),
@@ -449,8 +491,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             } else {
 #pragma unroll
               for (int i = 0; i < 32; i += 2) {
-                const float p0 = i > cm ? 0.f : exp2f(__uint_as_float(s[i]) - lse2);
-                const float p1 = i + 1 > cm ? 0.f : exp2f(__uint_as_float(s[i + 1]) - lse2);
+                const float p0 = (i >= l2 && i <= h2) ? exp2f(__uint_as_float(s[i]) - lse2) : 0.f;
+                const float p1 = (i + 1 >= l2 && i + 1 <= h2) ? exp2f(__uint_as_float(s[i + 1]) - lse2) : 0.f;
                 pk[hf * 16 + (i >> 1)] = pack2<T16>(p0, p1);
               }
             }
@@ -513,9 +555,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       return __all_sync(0xffffffffu, ok);
     };
     for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++item_count) {
-      int role, bh, q, nxt, ncs;
+      int role, bh, q, xt0, nxt;
       decode(item, role, bh, q);
-      tile_counts(q, nxt, ncs);
+      const Win win = role_win(role);
+      x_range(q, win, xt0, nxt);
       const size_t hb = (size_t)bh * T * D;
       const T16* Xg = (const T16*)p.x[role] + hb;
       const CUtensorMap* tmDX = role == 0 ? &tmDK2 : &tmDK1;
@@ -526,10 +569,11 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         if (row < D) dq_acc[row] = 0.f;
         if (!fold_sync()) { alive = false; break; }
       }
-      for (int xt = 0; xt < nxt && alive; ++xt, ++xt_count) {
+      for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
         const int x_r = xt * 128 + row;
-        const bool x_ok = (p.causal ? (x_r <= q) : true) && x_r < T;
-        const bool warp_rows_live = xt * 128 + wq * 32 <= (p.causal ? q : T - 1);
+        const bool x_ok = (p.causal ? (x_r <= q && q - x_r <= win.xw) : true) && x_r < T;
+        // (rows outside the query's range carry zeros: a warp whose 32 rows all are has nothing to add)
+        const bool warp_rows_live = __any_sync(0xffffffffu, x_ok);
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.gu_done, xt_count & 1, abort_flag));
         if (!alive) break;
         tc_fence_after();
@@ -573,7 +617,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             // likewise G
             tc_fence_before();
             mbar_arrive(&bars.g_free);
-            if (xt == nxt - 1) mbar_arrive(&bars.vec_free[item_count & 1]);  // and this query's vectors are done with
+            if (xt == xt0 + nxt - 1) mbar_arrive(&bars.vec_free[item_count & 1]);  // and this query's vectors are done with
           }
           uint8_t* slot = slots + (round & 1) * 4096;
           // the reduce-add issued two rounds ago from this slot must have finished reading it
@@ -650,6 +694,10 @@ int launch_bwd(const TdpArgs& a) {
   p.T = a.T; p.BN = BN; p.q_mod = a.q_mod; p.q_rem = a.q_rem;
   p.nq = a.q_rem < a.T ? (a.T - a.q_rem + a.q_mod - 1) / a.q_mod : 0;
   p.causal = a.mask.causal;
+  p.k1w = a.mask.k1w;
+  p.k2w = a.mask.k2w;
+  p.kkl = a.mask.kkl;
+  p.kkr = a.mask.kkr;
   p.alpha = a.alpha;
   p.status = a.status_word;
   if (p.nq > 0) {

@@ -64,10 +64,10 @@ def test_c_abi_rejects_bad_arguments_without_a_device():
 def test_tdp_path_selection():
     T = 512
     full = dict(causal=True, k1w=None, k2w=None, kkl=None, kkr=None)
-    # fp32 inputs always run on the general CUDA-core kernels; narrow windows do in the backward only
+    # fp32 inputs always run on the general CUDA-core kernels; 16-bit ones on the tensor cores under every mask
     assert _native.tdp_path(_native.OP_TDP_FWD, T, 64, _native.F32, **full) == _native.PATH_SIMT
     assert _native.tdp_path(_native.OP_TDP_FWD, T, 64, _native.BF16, True, 8, 8, 4, 4) == _native.PATH_TCGEN05
-    assert _native.tdp_path(_native.OP_TDP_BWD, T, 64, _native.BF16, True, 8, 8, 4, 4) == _native.PATH_SIMT
+    assert _native.tdp_path(_native.OP_TDP_BWD, T, 64, _native.BF16, True, 8, 8, 4, 4) == _native.PATH_TCGEN05
     assert _native.tdp_path(_native.OP_TDP_FWD, T, 64, _native.BF16, **full,
                             flags=_native.FLAG_FORCE_SIMT) == _native.PATH_SIMT
 

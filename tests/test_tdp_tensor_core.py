@@ -199,3 +199,27 @@ def test_forward_windows_large_logits_fp16():
     assert _native.read_status(torch.device(DEV)) == 0
     z_ref, _ = orc.tdp_forward(*(t.float() for t in (q, k1, k2, v1, v2)), 1 / 8, True, *windows)
     assert float((o.float().cpu() - z_ref).abs().max()) <= 1e-2
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("windows", WINDOWS)
+def test_backward_windows_match_oracle(windows, D):
+    """All five gradients under k1 / k2 windows and the (j, k) band, through the autograd entry point."""
+    B, N, T, dtype = 1, 2, 300, torch.bfloat16
+    alpha = 1.0 / D
+    q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, scale=0.5, seed=31 + D, dtype=dtype)
+    code = _native.dtype_code(dtype)
+    assert _native.tdp_path(_native.OP_TDP_BWD, T, D, code, True, *windows) == _native.PATH_TCGEN05
+    leaves = [x.to(DEV).requires_grad_(True) for x in (q, k1, k2, v1, v2)]
+    k1w, k2w, kkl, kkr = windows
+    out = flash_trittention(*leaves, alpha, kkl, kkr, k1w, k2w, True)
+    out.backward(dz.to(DEV))
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0, "a bounded barrier wait ran out"
+    f = [x.float() for x in (q, k1, k2, v1, v2)]
+    g_ref = orc.tdp_backward(*f, dz.float(), alpha, True, *windows)
+    for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, g_ref):
+        g = leaf.grad.float().cpu()
+        assert torch.isfinite(g).all(), name
+        err, mag = float((g - ref).abs().max()), float(ref.abs().max())
+        assert err <= TOL[dtype] * max(1.0, mag), (name, err, mag)
