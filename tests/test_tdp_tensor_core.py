@@ -223,3 +223,37 @@ def test_backward_windows_match_oracle(windows, D):
         assert torch.isfinite(g).all(), name
         err, mag = float((g - ref).abs().max()), float(ref.abs().max())
         assert err <= TOL[dtype] * max(1.0, mag), (name, err, mag)
+
+
+@pytest.mark.parametrize("windows", [(64, 150, 30, 10), (8, 8, 4, 4)])
+def test_windows_with_query_shards(windows):
+    """Query-row sharding under a windowed mask: forward shards write disjoint rows, backward shards leave fp32
+    partial key-side sums whose total, finalised once, equals the unsharded gradients."""
+    B, N, T, D, alpha = 1, 2, 300, 64, 1 / 64
+    q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, scale=0.5, seed=29, dtype=torch.bfloat16)
+    t = [x.to(DEV) for x in (q, k1, k2, v1, v2)]
+    do = dz.to(DEV)
+    o, lse = torch.empty_like(t[0]), torch.empty(B, N, T, device=DEV)
+    _native.tdp_fwd(*t, o, lse, alpha, True, *windows)
+    o2, lse2 = torch.zeros_like(o), torch.zeros_like(lse)
+    for rem in range(4):
+        _native.tdp_fwd(*t, o2, lse2, alpha, True, *windows, q_mod=4, q_rem=rem)
+    assert float((o2.float() - o.float()).abs().max()) <= 1e-2
+    assert float((lse2 - lse).abs().max()) <= 1e-3
+    full = [torch.empty_like(t[0]) for _ in range(5)]
+    _native.tdp_bwd(*t, o, do, lse, *full, alpha, True, *windows)
+    dq = torch.zeros_like(t[0])
+    n = t[0].numel()
+    acc = torch.zeros(4 * n, device=DEV)
+    for rem in range(4):
+        ws = _native.tdp_bwd(*t, o, do, lse, dq, None, None, None, None, alpha, True, *windows,
+                             q_mod=4, q_rem=rem, flags=_native.FLAG_BWD_PARTIAL)
+        acc += ws[: 16 * n].view(torch.float32)
+    ws = _native.workspace(_native.OP_TDP_BWD, B, N, T, D, _native.BF16, DEV)
+    ws[: 16 * n].view(torch.float32).copy_(acc)
+    outs = [torch.empty_like(t[0]) for _ in range(4)]
+    _native.tdp_bwd_finalize(t[3], *outs, ws)
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0
+    for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), [dq] + outs, full):
+        assert float((a.float() - b.float()).abs().max()) <= 2e-2 * max(1.0, float(b.float().abs().max())), name
