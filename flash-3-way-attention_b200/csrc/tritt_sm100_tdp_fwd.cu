@@ -170,6 +170,20 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     jt0 = ja / kBJ;
     njt = jb / kBJ - jt0 + 1;
   };
+  // Attended columns of k-tile kt (union over its rows): [ja, jb].  A slab whose attended columns all lie in one
+  // 64-column half (halves() = 1: the lower, 2: the upper, 0: both) runs as 128 x 64 score products and a 64-deep
+  // value product.
+  auto col_span = [&](int qa, int qb, int kt, int& ja, int& jb) {
+    ja = 0;
+    jb = T - 1;
+    if (p.causal) {
+      const int klo = max(0, max(qa - p.k2w, qa - p.k1w - p.kkr));
+      const int ka = max(kt * 128, klo), kb = min(kt * 128 + 127, qb);
+      ja = max(0, max(qa - p.k1w, ka - p.kkl));
+      jb = min(qb, kb + p.kkr);
+    }
+  };
+  auto halves = [](int ja, int jb, int j0) { return jb < j0 + 64 ? 1 : (ja >= j0 + 64 ? 2 : 0); };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -240,23 +254,43 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         return ok;
       };
       auto release = [&](uint32_t pos) { mma_commit(&bars.ring_empty[pos % NS]); };
-      // S_x = A_x * K1tile^T  (one chain of D/16 instructions)
-      auto issue_s = [&](int x, uint32_t pos) {
+      // S_x = A_x * K1tile^T  (one chain of D/16 instructions); hm != 0: only 64 rows of the key tile (the lower
+      // or the upper ones), scores in the first 64 columns of S_x
+      constexpr uint32_t idesc_s64 = make_idesc_f16(128, 64, kFmt, false, false);
+      auto issue_s = [&](int x, uint32_t pos, int hm) {
         const uint32_t bLo = ringK + (pos % NS) * kTile16;
+        if (hm == 0) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-          mma_ss_lo(tmem + x * kBJ, aLo[x] + kk, bLo + kk, kHi, idesc_s, k > 0);
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
+            mma_ss_lo(tmem + x * kBJ, aLo[x] + kk, bLo + kk, kHi, idesc_s, k > 0);
+          }
+        } else {
+          const uint32_t bRow = bLo + (hm == 2 ? (64 * 128) >> 4 : 0);   // rows 64.. of a 128-byte-pitch block
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
+            mma_ss_lo(tmem + x * kBJ, aLo[x] + kk, bRow + kk, kHi, idesc_s64, k > 0);
+          }
         }
         mma_commit(&bars.s_ready[x]);
       };
-      // acc_x (+)= P_x * SiLU(V1)tile  (one chain of 8 instructions; P_x overlays the first 64 columns of S_x)
-      auto issue_pv = [&](int x, uint32_t pos, uint32_t acc) {
+      // acc_x (+)= P_x * SiLU(V1)tile  (one chain of 8 instructions; P_x overlays the first 64 columns of S_x);
+      // hm != 0: P_x has 64 columns (4 instructions) and meets the lower or upper 64 rows of the value tile
+      auto issue_pv = [&](int x, uint32_t pos, uint32_t acc, int hm) {
         const uint32_t bLo = ringMN + (pos % NS) * kTile16;
+        if (hm == 0) {
 #pragma unroll
-        for (int k = 0; k < kBJ / 16; ++k)
-          mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv,
-                    k > 0 ? 1u : acc);
+          for (int k = 0; k < kBJ / 16; ++k)
+            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv,
+                      k > 0 ? 1u : acc);
+        } else {
+          const uint32_t bRow = bLo + (hm == 2 ? (4 * 2048) >> 4 : 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + k * 8, bRow + k * (2048 >> 4), kHi, idesc_pv,
+                      k > 0 ? 1u : acc);
+        }
       };
 
       for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
@@ -271,12 +305,16 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           FT(2)
           tc_fence_after();
           if (!wait_full(base)) { alive = false; break; }
-          issue_s(0, base);
-          issue_s(1, base);
+          int ja, jb;
+          col_span(qa, qb, kt, ja, jb);
+          int hm = halves(ja, jb, jt0 * kBJ);
+          issue_s(0, base, hm);
+          issue_s(1, base, hm);
           release(base);
           for (int jt = 0; jt < njt && alive; ++jt, ++n) {
             const uint32_t pv = base + 2 * jt + 1, pk = base + 2 * jt + 2;
             const bool more = jt + 1 < njt;
+            const int hm_next = more ? halves(ja, jb, (jt0 + jt + 1) * kBJ) : 0;
             for (int x = 0; x < 2 && alive; ++x) {
               FT(0)
               if (!mbar_wait(&bars.p_ready[x], n & 1, abort_flag)) { alive = false; break; }
@@ -288,14 +326,15 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
               }
               tc_fence_after();
               if (x == 0 && !wait_full(pv)) { alive = false; break; }
-              issue_pv(x, pv, jt > 0);
+              issue_pv(x, pv, jt > 0, hm);
               if (x == 1) release(pv);
               if (more) {
                 if (x == 0 && !wait_full(pk)) { alive = false; break; }
-                issue_s(x, pk);
+                issue_s(x, pk, hm_next);
                 if (x == 1) release(pk);
               }
             }
+            hm = hm_next;
           }
           if (alive) mma_commit(&bars.o_done);
           base += 2 * njt;
@@ -324,8 +363,9 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       const T16* Qg = (const T16*)p.q + (size_t)bh * T * D;
 
       for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
-        int jt0, njt;
+        int jt0, njt, ja, jb;
         j_range(qa, qb, kt, jt0, njt);
+        col_span(qa, qb, kt, ja, jb);
         // Columns this row may see: [c_lo, c_hi].  A row outside the k range of its query (its weight in the
         // fold is zero) keeps the query's own column range so that it never sees an empty one by construction;
         // a row inside can still see none in a slab, or at all: its maximum then stays -inf and its P zero.
@@ -384,13 +424,18 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           if (jt == njt - 1) mbar_arrive(&bars.a_free);  // the last score product of this k-tile has read A_x
           // this row's valid columns within the slab: [lo, hi]; the warp takes the unmasked path when every
           // row sees the whole slab
-          const int j0 = (jt0 + jt) * kBJ;
+          // A slab with attended columns in one 64-column half only was computed for that half alone: its scores
+          // are in the first 64 columns of S_x and stand for the slab's columns [coff, coff + 64).
+          const int hm = halves(ja, jb, (jt0 + jt) * kBJ);
+          const int nh = hm ? 1 : 2, coff = hm == 2 ? 64 : 0;
+          const int j0 = (jt0 + jt) * kBJ + coff;
           const int lo = c_lo - j0, hi = c_hi - j0;
-          const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= kBJ - 1);
+          const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 64 * nh - 1);
           // pass 1: row maximum
           float mx = -INFINITY;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
+            if (hf >= nh) break;
             uint32_t sr[64];
             tmem_ld64(tS + hf * 64, sr);
             tmem_wait_ld();
@@ -443,6 +488,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           float psum = 0.f;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
+            if (hf >= nh) break;
             uint32_t sr[64];
             tmem_ld64(tS + hf * 64, sr);
             tmem_wait_ld();
