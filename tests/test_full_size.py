@@ -1,7 +1,8 @@
-"""Parity at the sequence lengths and head dimensions of the benchmark configurations (T=2048, D=128 and
-T=4096, D=64, bf16, causal, alpha = 1/D), where the dense oracle cannot run: sampled query rows against an fp32
-per-row evaluation of the same formulas, and size-independent properties of the backward (linearity in the
-upstream gradient, query-row shards summing to the full gradient)."""
+"""Parity at the sequence lengths and head dimensions of the benchmark configurations, where the dense oracle
+cannot run.  Triple-dot-product (T=2048, D=128 and T=4096, D=64, bf16, causal, alpha = 1/D): sampled query rows
+against an fp32 per-row evaluation of the same formulas, and size-independent properties of the backward (linearity
+in the upstream gradient, query-row shards summing to the full gradient).  Dot-product-sum (T=1024, D=64, fp16):
+the whole result against the factorised fp32 formulation on the CPU."""
 import pytest
 import torch
 
@@ -118,3 +119,42 @@ def test_query_shards_sum_to_the_full_gradient_at_benchmark_size():
     for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), [dq] + outs, full):
         mag = max(1.0, float(b.float().abs().max()))
         assert float((a.float() - b.float()).abs().max()) <= TOL * mag, name
+
+
+def _dps_factorised(q, k1, k2, v1, v2, a, k_diff):
+    """Differentiable fp32 restatement of the dot-product-sum variant as two chained soft-max attentions
+    (inner over s per K2 row t, outer over t per query; causal, t - s <= k_diff), as in the oracle's
+    ``dps_forward_factorised``."""
+    T = q.shape[-2]
+    sv1 = torch.nn.functional.silu(v1)
+    E = a * torch.matmul(k1, k2.transpose(-1, -2))
+    s = torch.arange(T).view(-1, 1)
+    t = torch.arange(T).view(1, -1)
+    E = E.masked_fill(~((s <= t) & (t - s <= k_diff)), float("-inf"))
+    lse_in = torch.logsumexp(E, dim=-2)
+    Y = torch.matmul(torch.exp(E - lse_in[..., None, :]).transpose(-1, -2), sv1)
+    Fq = a * torch.matmul(q, k2.transpose(-1, -2)) + lse_in[..., None, :]
+    Fq = Fq.masked_fill(~(t <= s), float("-inf"))
+    lse = torch.logsumexp(Fq, dim=-1)
+    return torch.matmul(torch.exp(Fq - lse[..., None]), Y * v2), lse
+
+
+def test_dot_product_sum_at_benchmark_size():
+    """Config 3 shape per head (T=1024, D=64, fp16, alpha = 1/8, causal, k_diff = T), two heads."""
+    from flash_trittention.dot_product_sum.trittention_triton import TrittentionTriton
+
+    B, N, T, D, a = 1, 2, 1024, 64, 1 / 8
+    q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, seed=109, dtype=torch.float16)
+    leaves = [x.to(DEV).requires_grad_(True) for x in (q, k1, k2, v1, v2)]
+    out, m = TrittentionTriton(causal=True, softmax_scale=a, k_diff=T)(*leaves)
+    out.backward(dz.to(DEV))
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0
+    ref_leaves = [x.float().requires_grad_(True) for x in (q, k1, k2, v1, v2)]
+    z_ref, lse_ref = _dps_factorised(*ref_leaves, a, T)
+    z_ref.backward(dz.float())
+    assert float((out.detach().float().cpu() - z_ref.detach()).abs().max()) <= 5e-3
+    assert float((m.cpu() - lse_ref.detach()).abs().max()) <= 5e-3
+    for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, ref_leaves):
+        g, r = leaf.grad.float().cpu(), ref.grad
+        assert float((g - r).abs().max()) <= 5e-3 * max(1.0, float(r.abs().max())), name
