@@ -211,14 +211,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       auto load_stage = [&](const CUtensorMap* tm, int row0, int bh) -> bool {
         const int st = pos % NS;
         if (!mbar_wait(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag)) return false;
-#ifdef TRITT_EXP_NOTMA
-        mbar_arrive(&bars.ring_full[st]);
-        (void)tm; (void)row0; (void)bh;
-#else
         mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kTileA);
         for (int hh = 0; hh < KH; ++hh)
           tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kTileA + hh * 16384, tm, &bars.ring_full[st], hh * 64, row0, bh);
-#endif
         ++pos;
         return true;
       };
