@@ -151,6 +151,44 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def other_workloads(dev):
+    """Short CUDA-event timings of the other benchmark configurations on one GPU (not part of the headline
+    value): config 2 forward, the reference's banded forward case, config 3 (dot-product-sum) forward+backward."""
+    from flash_trittention import flash_trittention
+    from flash_trittention.dot_product_sum.trittention_triton import TrittentionTriton
+
+    def timed(fn, iters=5):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    out = {}
+    t = [x.to(dev) for x in _make_inputs(4, 8, 512, 64, 0.5, 2, torch.bfloat16)[:5]]
+    with torch.no_grad():
+        ms = timed(lambda: flash_trittention(*t, 1 / 64, None, None, None, None, True))
+    out["tdp_fwd_4x8x512x64_bf16"] = {"ms": ms, "tflops": _flops(4, 8, 512, 64, "fwd") / ms / 1e9}
+    t = [x.to(dev) for x in _make_inputs(2, 8, 2048, 64, 1.0, 3, torch.float16)[:5]]
+    with torch.no_grad():
+        ms = timed(lambda: flash_trittention(*t, 1 / 8, 32, 32, 128, 128, True))
+    out["tdp_fwd_2x8x2048x64_fp16_windows_128_128_32_32"] = {"ms": ms}
+    ins = [x.to(dev) for x in _make_inputs(2, 8, 1024, 64, 1.0, 4, torch.float16)]
+    mod = TrittentionTriton(causal=True, softmax_scale=1 / 8, k_diff=1024)
+
+    def dps_step():
+        leaves = [x.detach().requires_grad_(True) for x in ins[:5]]
+        o, _ = mod(*leaves)
+        o.backward(ins[5])
+
+    out["dps_fwd_bwd_2x8x1024x64_fp16"] = {"ms": timed(dps_step)}
+    return out
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -291,6 +329,8 @@ def run_ours(args):
             "traffic": 7.93e6 * per, "traffic_unit": "bytes per launch (ncu at 2 heads, scaled by heads)",
         },
     }
+    if world == 1 and not args.skip_cpu:
+        line["other_workloads"] = other_workloads(dev)
     if cpu_v is not None:
         line["cpu_baseline"] = {"value": cpu_v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                                 "sample": cpu_sample}
