@@ -4,6 +4,8 @@
 // combination.  It computes in fp32 and is what fp32 inputs and narrow-window calls run
 // on; the tensor-core path takes over for the shapes it supports.
 //
+// (Head dimensions 16, 32 and 64 run the register-resident variant in tritt_simt_tdp_quad.cuh: a quad of lanes
+// per pair row; the kernel below keeps the per-row vectors in shared memory and serves the other dimensions.)
 // One thread owns one "pair row" (q, x): x indexes K2/V2 (role 0) or K1/V1 (role 1) and
 // the thread walks the other key axis c, so that a row behaves like an ordinary
 // attention query with the pre-scaled vector a[h] = alpha*Q[q,h]*X[x,h]:
@@ -218,6 +220,8 @@ __global__ void tdp_simt_kernel(SimtTdpParams p) {
 #undef VEC
 }
 
+#include "tritt_simt_tdp_quad.cuh"
+
 template <typename T>
 __global__ void tdp_finalize_kernel(const T* v1, T* dk1, T* dk2, T* dv1, T* dv2, const float* part, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -239,8 +243,21 @@ size_t smem_bytes(int nvec, int D, int nt) {
   return ((size_t)nvec * D * nt + 2 * kTileC * D + 4 * D + 2 * nt) * sizeof(float);
 }
 
+template <typename T, int MODE, int DQ>
+int launch_quad(const SimtTdpParams& p, int BN, cudaStream_t stream) {
+  if (p.nq <= 0) return 0;
+  tdp_simt_quad_kernel<T, MODE, DQ><<<dim3(p.nq, BN), 128, 0, stream>>>(p);
+  count_launch();
+  TRITT_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 template <typename T, int MODE>
 int launch(const SimtTdpParams& p, int BN, cudaStream_t stream) {
+  // head dimensions 16, 32, 64: the register-resident kernels
+  if (p.D == 64) return launch_quad<T, MODE, 16>(p, BN, stream);
+  if (p.D == 32) return launch_quad<T, MODE, 8>(p, BN, stream);
+  if (p.D == 16) return launch_quad<T, MODE, 4>(p, BN, stream);
   constexpr int NV = num_vecs<MODE>();
   const int nt = pick_threads(NV, p.D);
   const size_t sm = smem_bytes(NV, p.D, nt);
