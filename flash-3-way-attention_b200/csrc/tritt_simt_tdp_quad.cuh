@@ -173,12 +173,21 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
         }
         continue;
       }
-#pragma unroll 4
-      for (int cc = 0; cc < kQuadCols; ++cc) {
+      // Columns go in groups of eight: a group no row of the warp attends is skipped; inside a group masked
+      // columns run with weight 0, so that the loads and shuffles of its columns can overlap.
+      for (int cg = 0; cg < kQuadCols; cg += 8) {
+        bool any_ok = false;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int c = c0 + cg + e;
+          any_ok = any_ok || (active && c >= clo && c <= chi && mk.valid(q, p.role == 0 ? c : x, p.role == 0 ? x : c));
+        }
+        if (!__any_sync(0xffffffffu, any_ok)) continue;
+#pragma unroll
+      for (int cc = cg; cc < cg + 8; ++cc) {
         const int c = c0 + cc;
         const int j = p.role == 0 ? c : x, k = p.role == 0 ? x : c;
         const bool ok = active && c >= clo && c <= chi && mk.valid(q, j, k);
-        if (!__any_sync(0xffffffffu, ok)) continue;
         const float4* k4 = reinterpret_cast<const float4*>(tK + cc * D + qd * DQ);
         const float4* v4 = reinterpret_cast<const float4*>(tV + cc * D + qd * DQ);
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
@@ -223,6 +232,7 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
             }
           }
         }
+      }
       }
     }
     // per-row epilogue (rows that are not active hold zeros)
