@@ -4,7 +4,7 @@
 // combination.  It computes in fp32 and is what fp32 inputs and narrow-window calls run
 // on; the tensor-core path takes over for the shapes it supports.
 //
-// (Head dimensions 16, 32 and 64 run the register-resident variant in tritt_simt_tdp_quad.cuh: a quad of lanes
+// (Head dimensions 16 to 128 run the register-resident variant in tritt_simt_tdp_quad.cuh: four or eight lanes
 // per pair row; the kernel below keeps the per-row vectors in shared memory and serves the other dimensions.)
 // One thread owns one "pair row" (q, x): x indexes K2/V2 (role 0) or K1/V1 (role 1) and
 // the thread walks the other key axis c, so that a row behaves like an ordinary
@@ -243,10 +243,10 @@ size_t smem_bytes(int nvec, int D, int nt) {
   return ((size_t)nvec * D * nt + 2 * kTileC * D + 4 * D + 2 * nt) * sizeof(float);
 }
 
-template <typename T, int MODE, int DQ>
+template <typename T, int MODE, int DQ, int LPR>
 int launch_quad(const SimtTdpParams& p, int BN, cudaStream_t stream) {
   if (p.nq <= 0) return 0;
-  tdp_simt_quad_kernel<T, MODE, DQ><<<dim3(p.nq, BN), 128, 0, stream>>>(p);
+  tdp_simt_quad_kernel<T, MODE, DQ, LPR><<<dim3(p.nq, BN), 128, 0, stream>>>(p);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   return 0;
@@ -254,10 +254,11 @@ int launch_quad(const SimtTdpParams& p, int BN, cudaStream_t stream) {
 
 template <typename T, int MODE>
 int launch(const SimtTdpParams& p, int BN, cudaStream_t stream) {
-  // head dimensions 16, 32, 64: the register-resident kernels
-  if (p.D == 64) return launch_quad<T, MODE, 16>(p, BN, stream);
-  if (p.D == 32) return launch_quad<T, MODE, 8>(p, BN, stream);
-  if (p.D == 16) return launch_quad<T, MODE, 4>(p, BN, stream);
+  // head dimensions 16 to 128: the register-resident kernels (four lanes per row, eight at 128)
+  if (p.D == 128) return launch_quad<T, MODE, 16, 8>(p, BN, stream);
+  if (p.D == 64) return launch_quad<T, MODE, 16, 4>(p, BN, stream);
+  if (p.D == 32) return launch_quad<T, MODE, 8, 4>(p, BN, stream);
+  if (p.D == 16) return launch_quad<T, MODE, 4, 4>(p, BN, stream);
   constexpr int NV = num_vecs<MODE>();
   const int nt = pick_threads(NV, p.D);
   const size_t sm = smem_bytes(NV, p.D, nt);

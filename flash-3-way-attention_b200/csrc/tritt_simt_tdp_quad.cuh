@@ -1,36 +1,38 @@
-// Register-resident variant of the general CUDA-core triple-dot-product kernel for head dimensions up to 64.
-// Four consecutive lanes (a "quad") own one pair row (q, x); each lane keeps a quarter of the head dimension of the
+// Register-resident variant of the general CUDA-core triple-dot-product kernel for head dimensions 16 to 128.
+// LPR consecutive lanes (four; eight for head dimension 128) own one pair row (q, x); each lane keeps its share of the
 // row's vectors (a = alpha*Q[q]*X[x], a' = dO[q]*Y[x], the G and U sums) in registers, dot products are finished
-// with two shuffles inside the quad, and the tiles of the column axis are staged in shared memory and read with
+// with two or three shuffles inside the group, and the tiles of the column axis are staged in shared memory and read with
 // broadcast 16-byte loads.  Same arithmetic, modes, masks and outputs as tdp_simt_kernel (which keeps the vectors
 // in shared memory and serves the other head dimensions); about an order of magnitude fewer instructions per
 // attended triple.  Included by tritt_simt_tdp.cu after SimtTdpParams and the MODE_* constants.
 #pragma once
 
-constexpr int kQuadRows = 32;   // pair rows per pass of a CTA (128 threads)
 constexpr int kQuadCols = 32;   // column-axis rows staged per step
 
-__device__ __forceinline__ float tdp_quad_sum(float v) {
+// sum over the LPR lanes that own one row
+template <int LPR> __device__ __forceinline__ float tdp_row_sum(float v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);
   v += __shfl_xor_sync(0xffffffffu, v, 2);
+  if (LPR == 8) v += __shfl_xor_sync(0xffffffffu, v, 4);
   return v;
 }
-// sum over the 8 quads of a warp that hold the same quarter of the head dimension
-__device__ __forceinline__ float tdp_quads_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 4);
+// sum over the row groups of a warp that hold the same share of the head dimension
+template <int LPR> __device__ __forceinline__ float tdp_rows_sum(float v) {
+  if (LPR == 4) v += __shfl_xor_sync(0xffffffffu, v, 4);
   v += __shfl_xor_sync(0xffffffffu, v, 8);
   v += __shfl_xor_sync(0xffffffffu, v, 16);
   return v;
 }
 
-template <typename T, int MODE, int DQ>
+template <typename T, int MODE, int DQ, int LPR>
 __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
-  constexpr int D = DQ * 4;
+  constexpr int D = DQ * LPR;
+  constexpr int kQuadRows = 128 / LPR;   // pair rows per pass of a CTA (128 threads)
   __shared__ __align__(16) float tK[kQuadCols * D];
   __shared__ __align__(16) float tV[kQuadCols * D];
   __shared__ float qs[D], qr[D], dor[D], outacc[D];
   __shared__ float red[128];
-  const int tid = threadIdx.x, lane = tid & 31, qd = tid & 3, T_ = p.T;
+  const int tid = threadIdx.x, lane = tid & 31, qd = tid & (LPR - 1), T_ = p.T;
   const int bh = blockIdx.y;
   const int qi = p.nq - 1 - (int)blockIdx.x;  // long rows first
   const int q = p.q_rem + qi * p.q_mod;
@@ -85,7 +87,7 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
   float m_run = -INFINITY, l_run = 0.f;  // MODE_LSE, base-2 units (the same in the four lanes of a quad)
 
   for (int xb = xlo; xb <= xhi; xb += kQuadRows) {
-    const int x = xb + (tid >> 2);
+    const int x = xb + tid / LPR;
     const bool active = x <= xhi;
     float a[DQ], ay[DQ], g[DQ], u[DQ];   // ay, g: MODE_BWD only; u: the P*V sum of MODE_FWD / MODE_BWD
 #pragma unroll
@@ -157,7 +159,7 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
             s2 = fmaf(a[4 * i + 2], kv.z, s2);
             s3 = fmaf(a[4 * i + 3], kv.w, s3);
           }
-          const float s = tdp_quad_sum((s0 + s1) + (s2 + s3));
+          const float s = tdp_row_sum<LPR>((s0 + s1) + (s2 + s3));
           sc[cc] = ok ? s : -INFINITY;
           tmax = fmaxf(tmax, sc[cc]);
         }
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
           s2 = fmaf(a[4 * i + 2], kv.z, s2);
           s3 = fmaf(a[4 * i + 3], kv.w, s3);
         }
-        const float s = tdp_quad_sum((s0 + s1) + (s2 + s3));
+        const float s = tdp_row_sum<LPR>((s0 + s1) + (s2 + s3));
         {
           const float pr = ok ? exp2f(s - lse2) : 0.f;
           float ds = 0.f;
@@ -213,7 +215,7 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
               d2 = fmaf(ay[4 * i + 2], vv.z, d2);
               d3 = fmaf(ay[4 * i + 3], vv.w, d3);
             }
-            const float dp = tdp_quad_sum((d0 + d1) + (d2 + d3));
+            const float dp = tdp_row_sum<LPR>((d0 + d1) + (d2 + d3));
             ds = pr * (dp - Dq);
           }
 #pragma unroll
@@ -241,8 +243,8 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
       for (int i = 0; i < DQ; ++i) {
         const int h = qd * DQ + i;
         float v = active ? u[i] * to_f(Yp[(size_t)x * D + h]) : 0.f;
-        v = tdp_quads_sum(v);
-        if (lane < 4) atomicAdd(&outacc[h], v);
+        v = tdp_rows_sum<LPR>(v);
+        if (lane < LPR) atomicAdd(&outacc[h], v);
       }
     } else if (MODE == MODE_BWD) {
       float* dX = p.dX + base + (size_t)x * D;
@@ -257,8 +259,8 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
         }
         if (p.role == 0) {
           float v = active ? gg * to_f(Xp[(size_t)x * D + h]) : 0.f;
-          v = tdp_quads_sum(v);
-          if (lane < 4) atomicAdd(&outacc[h], v);
+          v = tdp_rows_sum<LPR>(v);
+          if (lane < LPR) atomicAdd(&outacc[h], v);
         }
       }
     }
@@ -273,7 +275,7 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
     }
     const float M = red[0];
     __syncthreads();
-    // every row is held by four lanes: count it once
+    // every row is held by LPR lanes: count it once
     red[tid] = (qd != 0 || m_run == -INFINITY) ? 0.f : l_run * exp2f(m_run - M);
     __syncthreads();
     for (int s = 64; s > 0; s >>= 1) {

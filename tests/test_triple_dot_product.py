@@ -124,3 +124,18 @@ def test_non_contiguous_inputs_and_query_sharding():
         _native.tdp_fwd(dq, dk1, dk2, dv1, dv2, o, lse, scale, True, None, None, None, None, q_mod=2, q_rem=rem)
     torch.testing.assert_close(o.cpu(), z_ref, rtol=1e-4, atol=2e-5)
     torch.testing.assert_close(lse.cpu(), lse_ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("D", [8, 16, 64, 128, 256])
+def test_fp32_head_dims(D):
+    """Head dimensions on both CUDA-core kernel families: 16..128 run the register-resident kernels (four lanes
+    per pair row, eight at 128), the others the shared-memory kernel; windows included."""
+    B, N, T, scale = 1, 2, 70, 1 / 8
+    q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, scale=0.7, seed=40 + D)
+    for windows in ((T, T, T, T), (20, 33, 6, 11)):
+        k1w, k2w, kkl, kkr = windows
+        out, grads = _run(q, k1, k2, v1, v2, dz, softmax_scale=scale, k1_window=k1w, k2_window=k2w, kk_left=kkl,
+                          kk_right=kkr, causal=True)
+        z_ref, _ = orc.tdp_forward(q, k1, k2, v1, v2, scale, True, k1w, k2w, kkl, kkr)
+        g_ref = orc.tdp_backward(q, k1, k2, v1, v2, dz, scale, True, k1w, k2w, kkl, kkr)
+        _compare(out, grads, z_ref, g_ref, (1e-4, 3e-5), (1e-3, 2e-4))
