@@ -329,6 +329,13 @@ def run_ours(args):
             "traffic": 7.93e6 * per, "traffic_unit": "bytes per launch (ncu at 2 heads, scaled by heads)",
         },
     }
+    fwd_ach = _flops(1, per, T, D, "fwd") / statistics.median(fwd_ms) / 1e9
+    line["roofline_forward"] = {
+        "bound": "tensor", "kernel": "tdp_fwd_kernel<128, bf16>", "achieved": fwd_ach, "peak": peaks["sustained"],
+        "unit": "TFLOP/s", "frac": fwd_ach / peaks["sustained"], "frac_of_burst_peak": fwd_ach / peaks["burst"],
+        # 128-wide tiles on the diagonal of the causal mask (ratio for T=2048); no recomputation in the forward
+        "executed_over_algorithmic_flops": 1.095,
+    }
     if world == 1 and not args.skip_cpu:
         line["other_workloads"] = other_workloads(dev)
     if cpu_v is not None:
