@@ -7,11 +7,12 @@ imported lazily so that ``import flash_trittention`` works without a GPU.
 
 __version__ = "0.1.0"
 
-__all__ = ["flash_trittention", "TrittentionTriton"]
+__all__ = ["flash_trittention", "TrittentionTriton"]  # the reference's public names; TrittentionTDP is an extra
 
 _LAZY_ATTRS = {
     "flash_trittention": (".triple_dot_product.flash_trittention", "flash_trittention"),
     "TrittentionTriton": (".dot_product_sum.trittention_triton", "TrittentionTriton"),
+    "TrittentionTDP": (".ops", "TrittentionTDP"),  # torch.library operators + module (not in the reference)
 }
 
 

@@ -101,5 +101,11 @@ def flash_trittention(
             f"effect (got {input_precision!r}); matmuls run at the kernel's default precision.",
             stacklevel=2,
         )
+    if torch.compiler.is_compiling():
+        # one opaque graph node instead of tracing into the autograd function
+        from ..ops import tdp_attention
+
+        return tdp_attention(q, k1, k2, v1, v2, softmax_scale, causal, k1_window, k2_window, kk_left, kk_right,
+                             convert_to_float32)[0]
     return FlashTrittention.apply(q, k1, k2, v1, v2, softmax_scale, kk_left, kk_right, k1_window, k2_window, causal,
                                   convert_to_float32)
