@@ -96,6 +96,11 @@ int tritt_tdp_path(int op, int T, int D, int dtype, int causal, int k1_window, i
   return use_sm100(op, T, D, dtype, m, flags) ? TRITT_PATH_TCGEN05 : TRITT_PATH_SIMT;
 }
 
+int tritt_dps_path(int T, int D, int dtype, int k_diff, int flags) {
+  const bool tc = !(flags & TRITT_FLAG_FORCE_SIMT) && k_diff >= 0 && sm100_attn_fwd_supported(T, D, dtype);
+  return tc ? TRITT_PATH_TCGEN05 : TRITT_PATH_SIMT;
+}
+
 size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype) {
   if (B <= 0 || N <= 0 || T <= 0 || D <= 0) return 0;
   size_t a = 0, b = 0;

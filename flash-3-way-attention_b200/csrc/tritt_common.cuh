@@ -125,6 +125,25 @@ int sm100_tdp_bwd(const TdpArgs& a);
 size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype);
 size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D);
 
+// Two-way soft-max attention forward on the tensor cores (16-bit operands [BN, T, D], head dimension 64 or 128):
+// out[r] = softmax_c(alpha x[r].k[c] + bias[c]) v[c] over the columns with (not causal, or c <= r <= c + win).
+struct AttnTcArgs {
+  const void *xq, *kc, *vc;  // row operand, column keys, column values
+  const float* bias;         // [BN, T] per column, natural-log units, or null
+  float* out_f32;            // [BN, T, D] fp32 result, or null
+  void* out_t;               // the same in the operands' type, or null
+  const void* mul;           // with out_mul: out_mul = out * mul element-wise, in the operands' type
+  void* out_mul;
+  float* out_lse;            // [BN, T] natural-log log-sum-exp of the rows
+  int BN, T, D, dtype, causal, win;
+  float alpha;
+  int* status;
+  cudaStream_t stream;
+};
+bool sm100_attn_fwd_supported(int T, int D, int dtype);
+int sm100_attn_fwd(const AttnTcArgs& a);
+int sm100_silu_16(const void* in, void* out, size_t n, int dtype, cudaStream_t stream);  // out = SiLU(in), 16-bit
+
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace tritt

@@ -353,8 +353,16 @@ int run_attn(int kind, const AttnParams& p, int BN, cudaStream_t stream) {
 //   Dq [r] | dW [n] | g [r] | dY [n] | Dt [r] | dK2a [n] | dsV1 [n]
 struct DpsWs {
   float *Y, *lse_in, *Dq, *dW, *g, *dY, *Dt, *dK2a, *dsV1;
+  void *sv1_16, *w_16;  // tensor-core forward only: SiLU(V1) and Y*V2 in the inputs' 16-bit type
 };
-DpsWs carve(void* ws, size_t n, size_t r) {
+size_t dps_float_bytes(int op, size_t n, size_t r) {
+  return align_up((op == TRITT_OP_DPS_FWD ? n + r : 5 * n + 4 * r) * sizeof(float), 256);
+}
+// The tensor-core forward serves 16-bit inputs with head dimension 64 or 128 and a non-negative k_diff.
+bool dps_fwd_on_tensor_cores(const DpsArgs& a) {
+  return !(a.flags & TRITT_FLAG_FORCE_SIMT) && a.k_diff >= 0 && sm100_attn_fwd_supported(a.T, a.D, a.dtype);
+}
+DpsWs carve(void* ws, size_t n, size_t r, int op) {
   float* f = (float*)ws;
   DpsWs w;
   w.Y = f; f += n;
@@ -366,7 +374,31 @@ DpsWs carve(void* ws, size_t n, size_t r) {
   w.Dt = f; f += r;
   w.dK2a = f; f += n;
   w.dsV1 = f;
+  w.sv1_16 = (char*)ws + dps_float_bytes(op, n, r);
+  w.w_16 = (char*)w.sv1_16 + align_up(n * 2, 256);
   return w;
+}
+
+// Both legs of the forward on the tensor cores: Y (fp32), LSEin and the outer leg's value operand Y*V2; then,
+// unless `inner_only`, O and m.
+int dps_fwd_tensor_cores(const DpsArgs& a, const DpsWs& w, bool inner_only) {
+  const size_t n = (size_t)a.B * a.N * a.T * a.D;
+  int rc = sm100_silu_16(a.v1, w.sv1_16, n, a.dtype, a.stream);
+  if (rc) return rc;
+  AttnTcArgs t{};
+  t.xq = a.k2; t.kc = a.k1; t.vc = w.sv1_16;
+  t.out_f32 = w.Y; t.out_lse = w.lse_in;
+  if (!inner_only) { t.mul = a.v2; t.out_mul = w.w_16; }
+  t.BN = a.B * a.N; t.T = a.T; t.D = a.D; t.dtype = a.dtype; t.causal = a.causal; t.win = a.k_diff;
+  t.alpha = a.alpha; t.status = a.status_word; t.stream = a.stream;
+  if ((rc = sm100_attn_fwd(t)) || inner_only) return rc;
+  AttnTcArgs u{};
+  u.xq = a.q; u.kc = a.k2; u.vc = w.w_16;
+  u.bias = w.lse_in;
+  u.out_t = a.out_o; u.out_lse = a.out_m;
+  u.BN = a.B * a.N; u.T = a.T; u.D = a.D; u.dtype = a.dtype; u.causal = a.causal; u.win = a.T;
+  u.alpha = a.alpha; u.status = a.status_word; u.stream = a.stream;
+  return sm100_attn_fwd(u);
 }
 
 template <typename T>
@@ -384,7 +416,8 @@ int dps_inner_fwd(const DpsArgs& a, const DpsWs& w) {
 template <typename T>
 int dps_fwd_t(const DpsArgs& a) {
   const size_t n = (size_t)a.B * a.N * a.T * a.D, r = (size_t)a.B * a.N * a.T;
-  DpsWs w = carve(a.workspace, n, r);
+  DpsWs w = carve(a.workspace, n, r, TRITT_OP_DPS_FWD);
+  if (dps_fwd_on_tensor_cores(a)) return dps_fwd_tensor_cores(a, w, false);
   int rc = dps_inner_fwd<T>(a, w);
   if (rc) return rc;
   AttnParams p{};
@@ -401,10 +434,10 @@ int dps_fwd_t(const DpsArgs& a) {
 template <typename T>
 int dps_bwd_t(const DpsArgs& a) {
   const size_t n = (size_t)a.B * a.N * a.T * a.D, r = (size_t)a.B * a.N * a.T;
-  DpsWs w = carve(a.workspace, n, r);
+  DpsWs w = carve(a.workspace, n, r, TRITT_OP_DPS_BWD);
   const int BN = a.B * a.N;
   // inner leg again (Y, LSEin): cheaper than saving it between forward and backward
-  int rc = dps_inner_fwd<T>(a, w);
+  int rc = dps_fwd_on_tensor_cores(a) ? dps_fwd_tensor_cores(a, w, true) : dps_inner_fwd<T>(a, w);
   if (rc) return rc;
   rowdot_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
   count_launch();
@@ -461,10 +494,10 @@ int dps_bwd_t(const DpsArgs& a) {
 
 }  // namespace
 
-size_t simt_dps_workspace(int op, int B, int N, int T, int D, int /*dtype*/) {
+size_t simt_dps_workspace(int op, int B, int N, int T, int D, int dtype) {
   const size_t n = (size_t)B * N * T * D, r = (size_t)B * N * T;
-  if (op == TRITT_OP_DPS_FWD) return (n + r) * sizeof(float);
-  return (5 * n + 4 * r) * sizeof(float);
+  const size_t scratch16 = dtype == TRITT_F32 ? 0 : 2 * align_up(n * 2, 256);  // SiLU(V1), Y*V2
+  return dps_float_bytes(op, n, r) + scratch16;
 }
 
 int simt_dps_fwd(const DpsArgs& a) {

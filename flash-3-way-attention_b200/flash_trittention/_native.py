@@ -23,7 +23,7 @@ _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 # every symbol include/tritt.h declares
 SYMBOLS = (
-    "tritt_version", "tritt_kernel_launches", "tritt_last_error", "tritt_workspace_bytes", "tritt_tdp_path", "tritt_tdp_fwd",
+    "tritt_version", "tritt_kernel_launches", "tritt_last_error", "tritt_workspace_bytes", "tritt_tdp_path", "tritt_dps_path", "tritt_tdp_fwd",
     "tritt_tdp_bwd", "tritt_tdp_bwd_finalize", "tritt_tdp_bwd_partials_offset", "tritt_dps_fwd",
     "tritt_dps_bwd", "tritt_selftest_umma", "tritt_tdp_fwd_noalloc", "tritt_noalloc_scratch_bytes",
 )
@@ -57,6 +57,8 @@ def lib():
                 L.tritt_workspace_bytes.argtypes = [i] * 6
                 L.tritt_tdp_path.restype = i
                 L.tritt_tdp_path.argtypes = [i] * 10
+                L.tritt_dps_path.restype = i
+                L.tritt_dps_path.argtypes = [i] * 5
                 L.tritt_tdp_bwd_partials_offset.restype = sz
                 L.tritt_tdp_bwd_partials_offset.argtypes = [i] * 5
                 L.tritt_tdp_fwd.restype = i
@@ -128,6 +130,10 @@ def _win(w, T):
 def tdp_path(op, T, D, dtype, causal, k1w, k2w, kkl, kkr, flags=0) -> int:
     return lib().tritt_tdp_path(op, T, D, dtype, int(bool(causal)), _win(k1w, T), _win(k2w, T), _win(kkl, T),
                                 _win(kkr, T), flags)
+
+
+def dps_path(T, D, dtype, k_diff, flags=0) -> int:
+    return lib().tritt_dps_path(T, D, dtype, int(k_diff), flags)
 
 
 def tdp_fwd(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr, q_mod=1, q_rem=0, flags=0):

@@ -59,6 +59,9 @@ size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype);
 /* Which kernel family a TDP call with these arguments runs on. */
 int tritt_tdp_path(int op, int T, int D, int dtype, int causal, int k1_window, int k2_window, int kk_left,
                    int kk_right, int flags);
+/* Which kernel family the two soft-max attentions of a DPS forward run on (the backward recomputes its inner leg on
+   the same family and differentiates on the CUDA cores). */
+int tritt_dps_path(int T, int D, int dtype, int k_diff, int flags);
 
 /*
  * Triple-dot-product forward.  Replaces the launch of `_tritt_fwd` and the host-side

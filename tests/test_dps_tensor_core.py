@@ -1,0 +1,81 @@
+"""Dot-product-sum trittention with its two soft-max attentions on the tcgen05 kernel (16-bit inputs, head dimension
+64 or 128): forward against the oracle's factorised fp32 restatement and against the CUDA-core path, over ragged
+sequence lengths, narrow and wide ``k_diff`` bands, causal and not, large logits; and the backward, whose inner leg
+is recomputed by the same kernel.  Tolerances: max-abs 5e-3 (fp16) / 2e-2 (bf16), relative to max(1, magnitude)."""
+import pytest
+import torch
+
+from flash_trittention import _native
+from oracle import trittention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = {torch.float16: 5e-3, torch.bfloat16: 2e-2}
+
+
+def _fwd(t, scale, causal, k_diff, flags=0):
+    o = torch.empty_like(t[0])
+    m = torch.empty(t[0].shape[:3], dtype=torch.float32, device=DEV)
+    _native.dps_fwd(*t, o, m, scale, causal, k_diff, flags=flags)
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0
+    return o, m
+
+
+def test_path_selection():
+    assert _native.dps_path(1024, 64, _native.F16, 1024) == _native.PATH_TCGEN05
+    assert _native.dps_path(100, 128, _native.BF16, 0) == _native.PATH_TCGEN05
+    assert _native.dps_path(100, 32, _native.BF16, 8) == _native.PATH_SIMT
+    assert _native.dps_path(100, 64, _native.F32, 8) == _native.PATH_SIMT
+    assert _native.dps_path(100, 64, _native.F16, 8, _native.FLAG_FORCE_SIMT) == _native.PATH_SIMT
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("T,D,causal,k_diff", [
+    (33, 64, True, 33), (100, 64, True, 8), (128, 64, True, 0), (129, 128, True, 129), (300, 64, True, 130),
+    (300, 128, True, 2), (512, 64, True, 512), (384, 128, True, 200), (100, 64, False, 100), (260, 128, False, 5),
+])
+def test_forward_matches_oracle(dtype, T, D, causal, k_diff):
+    B, N, scale = 1, 2, 1 / 8
+    q, k1, k2, v1, v2, _ = orc.make_inputs(B, N, T, D, seed=T + D, dtype=dtype)
+    t = [x.to(DEV) for x in (q, k1, k2, v1, v2)]
+    assert _native.dps_path(T, D, _native.dtype_code(dtype), k_diff) == _native.PATH_TCGEN05
+    o, m = _fwd(t, scale, causal, k_diff)
+    z_ref, lse_ref = orc.dps_forward_factorised(*[x.float() for x in (q, k1, k2, v1, v2)], scale, causal, k_diff)
+    tol = TOL[dtype]
+    assert float((o.float().cpu() - z_ref).abs().max()) <= tol * max(1.0, float(z_ref.abs().max()))
+    assert float((m.cpu() - lse_ref).abs().max()) <= tol
+    # and against the CUDA-core kernels on the same inputs
+    o2, m2 = _fwd(t, scale, causal, k_diff, flags=_native.FLAG_FORCE_SIMT)
+    assert float((o.float() - o2.float()).abs().max()) <= tol * max(1.0, float(z_ref.abs().max()))
+    assert float((m - m2).abs().max()) <= tol
+
+
+def test_large_logits_stay_finite():
+    """Keys scaled by 8 (the reference's overflow guard, tests/test_dot_product_sum.py:84-118): logits of several
+    hundred, exponentials taken against the running row maximum."""
+    B, N, T, D, scale = 1, 2, 200, 64, 1 / 8
+    q, k1, k2, v1, v2, _ = orc.make_inputs(B, N, T, D, seed=5, dtype=torch.float16)
+    k1, k2 = k1 * 8, k2 * 8
+    t = [x.to(DEV) for x in (q, k1, k2, v1, v2)]
+    o, m = _fwd(t, scale, True, T)
+    assert torch.isfinite(o).all() and torch.isfinite(m).all()
+    z_ref, lse_ref = orc.dps_forward_factorised(*[x.float() for x in (q, k1, k2, v1, v2)], scale, True, T)
+    assert float((o.float().cpu() - z_ref).abs().max()) <= 5e-3 * max(1.0, float(z_ref.abs().max()))
+    assert float((m.cpu() - lse_ref).abs().max()) <= 5e-3 * max(1.0, float(lse_ref.abs().max()))
+
+
+@pytest.mark.parametrize("dtype,T,D,k_diff", [(torch.float16, 200, 64, 200), (torch.bfloat16, 160, 128, 12)])
+def test_backward_with_the_inner_leg_on_tensor_cores(dtype, T, D, k_diff):
+    from flash_trittention import TrittentionTriton
+
+    B, N, scale = 1, 2, 1 / 8
+    q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, seed=11, dtype=dtype)
+    leaves = [x.to(DEV).requires_grad_(True) for x in (q, k1, k2, v1, v2)]
+    out, _ = TrittentionTriton(causal=True, softmax_scale=scale, k_diff=k_diff)(*leaves)
+    out.backward(dz.to(DEV))
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0
+    g_ref = orc.dps_backward(*[x.float() for x in (q, k1, k2, v1, v2, dz)], scale, True, k_diff)
+    for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, g_ref):
+        assert float((leaf.grad.float().cpu() - ref).abs().max()) <= TOL[dtype] * max(1.0, float(ref.abs().max())), name
