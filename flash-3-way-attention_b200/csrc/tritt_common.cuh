@@ -144,6 +144,26 @@ bool sm100_attn_fwd_supported(int T, int D, int dtype);
 int sm100_attn_fwd(const AttnTcArgs& a);
 int sm100_silu_16(const void* in, void* out, size_t n, int dtype, cudaStream_t stream);  // out = SiLU(in), 16-bit
 
+// Backward of the same attention, as a row-owner and a column-owner kernel.  With P = exp(alpha x.k + bias - lse),
+// dP = dout.v and dS = P (dP - drow):  rows: d_rows_t = alpha sum_c dS k (+ d_rows_add);  columns: d_vc_f32 =
+// sum_r P dout, d_kc = alpha sum_r dS x (fp32 or the operands' type), gsum = sum_r dS.
+struct AttnBwdTcArgs {
+  const void *xq, *kc, *vc, *dout;  // 16-bit [BN, T, D]
+  const float *bias, *lse, *drow;   // [BN, T]: per column (or null), per row, per row
+  void* d_rows_t;
+  const float* d_rows_add;          // [BN, T, D] or null
+  float* d_kc_f32;
+  void* d_kc_t;
+  float* d_vc_f32;
+  float* gsum;                      // [BN, T] or null
+  int BN, T, D, dtype, causal, win;
+  float alpha;
+  int* status;
+  cudaStream_t stream;
+};
+int sm100_attn_bwd_rows(const AttnBwdTcArgs& a);
+int sm100_attn_bwd_cols(const AttnBwdTcArgs& a);
+
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace tritt

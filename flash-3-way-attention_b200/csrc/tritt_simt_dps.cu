@@ -274,7 +274,7 @@ __global__ void rowdot_kernel(const T* a, const T* b, float* out, size_t rows, i
 // dY = dW*V2; the inner attention's row term is Dt = sum_h dY*Y - g.
 template <typename T>
 __global__ void dps_mid_kernel(const float* dW, const float* Y, const T* v2, const float* g, T* dv2, float* dY,
-                               float* Dt, size_t rows, int D) {
+                               float* Dt, size_t rows, int D, T* dY_t = nullptr) {
   size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float acc = 0.f;
@@ -284,6 +284,7 @@ __global__ void dps_mid_kernel(const float* dW, const float* Y, const T* v2, con
     dv2[i] = from_f<T>(dw * y);
     const float dy = dw * to_f(v2[i]);
     dY[i] = dy;
+    if (dY_t) dY_t[i] = from_f<T>(dy);  // operand of the tensor-core inner backward
     acc += dy * y;
   }
   Dt[r] = acc - g[r];
@@ -353,7 +354,7 @@ int run_attn(int kind, const AttnParams& p, int BN, cudaStream_t stream) {
 //   Dq [r] | dW [n] | g [r] | dY [n] | Dt [r] | dK2a [n] | dsV1 [n]
 struct DpsWs {
   float *Y, *lse_in, *Dq, *dW, *g, *dY, *Dt, *dK2a, *dsV1;
-  void *sv1_16, *w_16;  // tensor-core forward only: SiLU(V1) and Y*V2 in the inputs' 16-bit type
+  void *sv1_16, *w_16, *dy_16;  // tensor-core path only: SiLU(V1), Y*V2 and dY in the inputs' 16-bit type
 };
 size_t dps_float_bytes(int op, size_t n, size_t r) {
   return align_up((op == TRITT_OP_DPS_FWD ? n + r : 5 * n + 4 * r) * sizeof(float), 256);
@@ -376,6 +377,7 @@ DpsWs carve(void* ws, size_t n, size_t r, int op) {
   w.dsV1 = f;
   w.sv1_16 = (char*)ws + dps_float_bytes(op, n, r);
   w.w_16 = (char*)w.sv1_16 + align_up(n * 2, 256);
+  w.dy_16 = (char*)w.w_16 + align_up(n * 2, 256);  // (backward only)
   return w;
 }
 
@@ -388,7 +390,7 @@ int dps_fwd_tensor_cores(const DpsArgs& a, const DpsWs& w, bool inner_only) {
   AttnTcArgs t{};
   t.xq = a.k2; t.kc = a.k1; t.vc = w.sv1_16;
   t.out_f32 = w.Y; t.out_lse = w.lse_in;
-  if (!inner_only) { t.mul = a.v2; t.out_mul = w.w_16; }
+  t.mul = a.v2; t.out_mul = w.w_16;
   t.BN = a.B * a.N; t.T = a.T; t.D = a.D; t.dtype = a.dtype; t.causal = a.causal; t.win = a.k_diff;
   t.alpha = a.alpha; t.status = a.status_word; t.stream = a.stream;
   if ((rc = sm100_attn_fwd(t)) || inner_only) return rc;
@@ -431,13 +433,58 @@ int dps_fwd_t(const DpsArgs& a) {
   return run_attn<T>(ATTN_FWD, p, a.B * a.N, a.stream);
 }
 
+// Backward with every attention product on the tensor cores (same eligibility as the forward).
+template <typename T>
+int dps_bwd_tensor_cores(const DpsArgs& a, const DpsWs& w) {
+  const size_t n = (size_t)a.B * a.N * a.T * a.D, r = (size_t)a.B * a.N * a.T;
+  int rc = dps_fwd_tensor_cores(a, w, true);  // Y, LSEin, Y*V2 again: cheaper than saving them
+  if (rc) return rc;
+  rowdot_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
+  count_launch();
+  TRITT_CUDA_OK(cudaGetLastError());
+  // ---- outer attention: rows q (Q), columns t (K2, W = Y*V2, bias LSEin)
+  AttnBwdTcArgs o{};
+  o.xq = a.q; o.kc = a.k2; o.vc = w.w_16; o.dout = a.d_o;
+  o.bias = w.lse_in; o.lse = a.m_in; o.drow = w.Dq;
+  o.BN = a.B * a.N; o.T = a.T; o.D = a.D; o.dtype = a.dtype; o.causal = a.causal; o.win = a.T;
+  o.alpha = a.alpha; o.status = a.status_word; o.stream = a.stream;
+  AttnBwdTcArgs orow = o;
+  orow.d_rows_t = a.dq;
+  if ((rc = sm100_attn_bwd_rows(orow))) return rc;
+  AttnBwdTcArgs ocol = o;
+  ocol.d_kc_f32 = w.dK2a; ocol.d_vc_f32 = w.dW; ocol.gsum = w.g;
+  if ((rc = sm100_attn_bwd_cols(ocol))) return rc;
+  dps_mid_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>(w.dW, w.Y, (const T*)a.v2, w.g, (T*)a.dv2, w.dY,
+                                                                        w.Dt, r, a.D, (T*)w.dy_16);
+  count_launch();
+  TRITT_CUDA_OK(cudaGetLastError());
+  // ---- inner attention: rows t (K2), columns s (K1, SiLU(V1)); upstream gradient dY
+  AttnBwdTcArgs i{};
+  i.xq = a.k2; i.kc = a.k1; i.vc = w.sv1_16; i.dout = w.dy_16;
+  i.lse = w.lse_in; i.drow = w.Dt;
+  i.BN = a.B * a.N; i.T = a.T; i.D = a.D; i.dtype = a.dtype; i.causal = a.causal; i.win = a.k_diff;
+  i.alpha = a.alpha; i.status = a.status_word; i.stream = a.stream;
+  AttnBwdTcArgs irow = i;
+  irow.d_rows_t = a.dk2;      // dK2 = (as outer key) + (as inner query)
+  irow.d_rows_add = w.dK2a;
+  if ((rc = sm100_attn_bwd_rows(irow))) return rc;
+  AttnBwdTcArgs icol = i;
+  icol.d_kc_t = a.dk1; icol.d_vc_f32 = w.dsV1;
+  if ((rc = sm100_attn_bwd_cols(icol))) return rc;
+  dps_dv1_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, a.stream>>>(w.dsV1, (const T*)a.v1, (T*)a.dv1, n);
+  count_launch();
+  TRITT_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 template <typename T>
 int dps_bwd_t(const DpsArgs& a) {
   const size_t n = (size_t)a.B * a.N * a.T * a.D, r = (size_t)a.B * a.N * a.T;
   DpsWs w = carve(a.workspace, n, r, TRITT_OP_DPS_BWD);
+  if (dps_fwd_on_tensor_cores(a)) return dps_bwd_tensor_cores<T>(a, w);
   const int BN = a.B * a.N;
   // inner leg again (Y, LSEin): cheaper than saving it between forward and backward
-  int rc = dps_fwd_on_tensor_cores(a) ? dps_fwd_tensor_cores(a, w, true) : dps_inner_fwd<T>(a, w);
+  int rc = dps_inner_fwd<T>(a, w);
   if (rc) return rc;
   rowdot_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
   count_launch();
@@ -496,7 +543,8 @@ int dps_bwd_t(const DpsArgs& a) {
 
 size_t simt_dps_workspace(int op, int B, int N, int T, int D, int dtype) {
   const size_t n = (size_t)B * N * T * D, r = (size_t)B * N * T;
-  const size_t scratch16 = dtype == TRITT_F32 ? 0 : 2 * align_up(n * 2, 256);  // SiLU(V1), Y*V2
+  // SiLU(V1), Y*V2 and (backward) dY in the inputs' type
+  const size_t scratch16 = dtype == TRITT_F32 ? 0 : (op == TRITT_OP_DPS_FWD ? 2 : 3) * align_up(n * 2, 256);
   return dps_float_bytes(op, n, r) + scratch16;
 }
 
