@@ -261,13 +261,17 @@ __global__ void attn_bwd_col_kernel(AttnParams p) {
 }
 
 // Dq[r] = sum_h dO*O  (reference dot_product_sum/kernels/bwd_preprocess.py:5-49)
+// out[r] = sum_h a[r,h] b[r,h]; a warp per row, so that consecutive lanes read consecutive elements
 template <typename T>
 __global__ void rowdot_kernel(const T* a, const T* b, float* out, size_t rows, int D) {
-  size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
   if (r >= rows) return;
   float s = 0.f;
-  for (int h = 0; h < D; ++h) s += to_f(a[r * D + h]) * to_f(b[r * D + h]);
-  out[r] = s;
+  for (int h = lane; h < D; h += 32) s += to_f(a[r * D + h]) * to_f(b[r * D + h]);
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) out[r] = s;
 }
 
 // Between the two backward attentions: dW (gradient of Y*V2) splits into dV2 = dW*Y and
@@ -275,10 +279,12 @@ __global__ void rowdot_kernel(const T* a, const T* b, float* out, size_t rows, i
 template <typename T>
 __global__ void dps_mid_kernel(const float* dW, const float* Y, const T* v2, const float* g, T* dv2, float* dY,
                                float* Dt, size_t rows, int D, T* dY_t = nullptr) {
-  size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // a warp per row, so that consecutive lanes touch consecutive elements
+  const size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
   if (r >= rows) return;
   float acc = 0.f;
-  for (int h = 0; h < D; ++h) {
+  for (int h = lane; h < D; h += 32) {
     const size_t i = r * D + h;
     const float dw = dW[i], y = Y[i];
     dv2[i] = from_f<T>(dw * y);
@@ -287,7 +293,9 @@ __global__ void dps_mid_kernel(const float* dW, const float* Y, const T* v2, con
     if (dY_t) dY_t[i] = from_f<T>(dy);  // operand of the tensor-core inner backward
     acc += dy * y;
   }
-  Dt[r] = acc - g[r];
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) Dt[r] = acc - g[r];
 }
 
 template <typename T>
@@ -439,7 +447,7 @@ int dps_bwd_tensor_cores(const DpsArgs& a, const DpsWs& w) {
   const size_t n = (size_t)a.B * a.N * a.T * a.D, r = (size_t)a.B * a.N * a.T;
   int rc = dps_fwd_tensor_cores(a, w, true);  // Y, LSEin, Y*V2 again: cheaper than saving them
   if (rc) return rc;
-  rowdot_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
+  rowdot_kernel<T><<<(unsigned)((r + 3) / 4), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   // ---- outer attention: rows q (Q), columns t (K2, W = Y*V2, bias LSEin)
@@ -454,7 +462,7 @@ int dps_bwd_tensor_cores(const DpsArgs& a, const DpsWs& w) {
   AttnBwdTcArgs ocol = o;
   ocol.d_kc_f32 = w.dK2a; ocol.d_vc_f32 = w.dW; ocol.gsum = w.g;
   if ((rc = sm100_attn_bwd_cols(ocol))) return rc;
-  dps_mid_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>(w.dW, w.Y, (const T*)a.v2, w.g, (T*)a.dv2, w.dY,
+  dps_mid_kernel<T><<<(unsigned)((r + 3) / 4), 128, 0, a.stream>>>(w.dW, w.Y, (const T*)a.v2, w.g, (T*)a.dv2, w.dY,
                                                                         w.Dt, r, a.D, (T*)w.dy_16);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
@@ -486,7 +494,7 @@ int dps_bwd_t(const DpsArgs& a) {
   // inner leg again (Y, LSEin): cheaper than saving it between forward and backward
   int rc = dps_inner_fwd<T>(a, w);
   if (rc) return rc;
-  rowdot_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
+  rowdot_kernel<T><<<(unsigned)((r + 3) / 4), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   // ---- outer attention: rows q (Q), columns t (K2, W = Y*V2, bias LSEin)
@@ -509,7 +517,7 @@ int dps_bwd_t(const DpsArgs& a) {
   pc.gsum = w.g;
   rc = run_attn<T>(ATTN_BWD_COL, pc, BN, a.stream);
   if (rc) return rc;
-  dps_mid_kernel<T><<<(unsigned)((r + 127) / 128), 128, 0, a.stream>>>(w.dW, w.Y, (const T*)a.v2, w.g, (T*)a.dv2, w.dY,
+  dps_mid_kernel<T><<<(unsigned)((r + 3) / 4), 128, 0, a.stream>>>(w.dW, w.Y, (const T*)a.v2, w.g, (T*)a.dv2, w.dY,
                                                                         w.Dt, r, a.D);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
