@@ -357,8 +357,14 @@ def main():
     ap.add_argument("--seq", type=int, default=WORK["T"], help="other sequence length, for profiler captures only")
     ap.add_argument("--skip-e2e", action="store_true", help="profiler captures: no host-copy pass")
     ap.add_argument("--skip-cpu", action="store_true", help="profiler captures: no CPU baseline sample")
+    ap.add_argument("--only-other", action="store_true",
+                    help="profiler captures: only the short timings of the other configurations (one GPU)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.only_other:
+        dev = torch.device("cuda:0")
+        torch.cuda.set_device(dev)
+        print(json.dumps({"other_workloads": other_workloads(dev)}))
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
