@@ -119,6 +119,13 @@ def workspace(op: int, B: int, N: int, T: int, D: int, dtype: int, device) -> to
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
 
+def aligned(t: torch.Tensor) -> torch.Tensor:
+    """``t`` made contiguous and, if its storage offset leaves it off a 16-byte boundary (a view into a larger
+    buffer), copied: the library's vector and TMA accesses require that alignment and reject other pointers."""
+    t = t.contiguous()
+    return t if t.data_ptr() % 16 == 0 else t.clone(memory_format=torch.contiguous_format)
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 

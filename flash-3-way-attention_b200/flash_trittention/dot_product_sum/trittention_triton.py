@@ -33,7 +33,7 @@ class TrittentionTritonFunction(torch.autograd.Function):
         if not q.is_cuda:
             raise RuntimeError("TrittentionTriton runs on CUDA tensors only (there is no CPU path)")
         _native.dtype_code(q.dtype)
-        q, k1, k2, v1, v2 = (t.contiguous() for t in (q, k1, k2, v1, v2))
+        q, k1, k2, v1, v2 = (_native.aligned(t) for t in (q, k1, k2, v1, v2))
         o = torch.empty_like(q)
         m = torch.empty(q.shape[:3], device=q.device, dtype=torch.float32)
         _native.dps_fwd(q, k1, k2, v1, v2, o, m, softmax_scale, causal, k_diff)
@@ -50,7 +50,7 @@ class TrittentionTritonFunction(torch.autograd.Function):
         assert grad_output.shape == o.shape, f"Shape mismatch: O={o.shape}, dO={grad_output.shape}"
         assert o.device == grad_output.device, "O and dO must be on the same device"
         assert o.dtype == grad_output.dtype, "O and dO must have the same dtype"
-        grad_output = grad_output.contiguous()
+        grad_output = _native.aligned(grad_output)
         dq, dk1, dk2, dv1, dv2 = (torch.empty_like(q) for _ in range(5))
         _native.dps_bwd(q, k1, k2, v1, v2, o, grad_output, m, dq, dk1, dk2, dv1, dv2, ctx.softmax_scale,
                         ctx.causal, ctx.k_diff)

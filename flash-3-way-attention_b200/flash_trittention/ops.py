@@ -51,7 +51,7 @@ def tdp_fwd(q: Tensor, k1: Tensor, k2: Tensor, v1: Tensor, v2: Tensor, softmax_s
     """``(o [B,N,T,D], lse [B,N,T] fp32)`` of ``tritt_tdp_fwd``; a window of ``None`` spans the sequence."""
     _check_inputs(q, k1, k2, v1, v2)
     _native.dtype_code(q.dtype)
-    q, k1, k2, v1, v2 = (t.contiguous() for t in (q, k1, k2, v1, v2))
+    q, k1, k2, v1, v2 = (_native.aligned(t) for t in (q, k1, k2, v1, v2))
     o = torch.empty_like(q)
     lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
     flags = _native.FLAG_FORCE_SIMT if convert_to_float32 else 0
@@ -73,8 +73,8 @@ def tdp_bwd(q: Tensor, k1: Tensor, k2: Tensor, v1: Tensor, v2: Tensor, o: Tensor
             kk_left: Optional[int], kk_right: Optional[int],
             convert_to_float32: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
     """``(dq, dk1, dk2, dv1, dv2)`` of ``tritt_tdp_bwd`` for the upstream gradient ``d_o`` of ``o``."""
-    q, k1, k2, v1, v2, o, lse = (t.contiguous() for t in (q, k1, k2, v1, v2, o, lse))
-    d_o = d_o.to(q.dtype).contiguous()
+    q, k1, k2, v1, v2, o, lse = (_native.aligned(t) for t in (q, k1, k2, v1, v2, o, lse))
+    d_o = _native.aligned(d_o.to(q.dtype))
     grads = tuple(torch.empty_like(q) for _ in range(5))
     flags = _native.FLAG_FORCE_SIMT if convert_to_float32 else 0
     _native.tdp_bwd(q, k1, k2, v1, v2, o, d_o, lse, *grads, softmax_scale, causal, k1_window, k2_window, kk_left,
@@ -120,7 +120,7 @@ def dps_fwd(q: Tensor, k1: Tensor, k2: Tensor, v1: Tensor, v2: Tensor, softmax_s
     """``(o [B,N,S,D], m [B,N,S] fp32 log-sum-exp)`` of ``tritt_dps_fwd``."""
     _check_inputs(q, k1, k2, v1, v2)
     _native.dtype_code(q.dtype)
-    q, k1, k2, v1, v2 = (t.contiguous() for t in (q, k1, k2, v1, v2))
+    q, k1, k2, v1, v2 = (_native.aligned(t) for t in (q, k1, k2, v1, v2))
     o = torch.empty_like(q)
     m = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
     _native.dps_fwd(q, k1, k2, v1, v2, o, m, softmax_scale, causal, k_diff)
@@ -137,8 +137,8 @@ def _(q, k1, k2, v1, v2, softmax_scale, causal, k_diff):
 @torch.library.custom_op("flash_trittention::dps_bwd", mutates_args=(), device_types="cuda")
 def dps_bwd(q: Tensor, k1: Tensor, k2: Tensor, v1: Tensor, v2: Tensor, o: Tensor, d_o: Tensor, m: Tensor,
             softmax_scale: float, causal: bool, k_diff: int) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
-    q, k1, k2, v1, v2, o, m = (t.contiguous() for t in (q, k1, k2, v1, v2, o, m))
-    d_o = d_o.to(q.dtype).contiguous()
+    q, k1, k2, v1, v2, o, m = (_native.aligned(t) for t in (q, k1, k2, v1, v2, o, m))
+    d_o = _native.aligned(d_o.to(q.dtype))
     grads = tuple(torch.empty_like(q) for _ in range(5))
     _native.dps_bwd(q, k1, k2, v1, v2, o, d_o, m, *grads, softmax_scale, causal, k_diff)
     return grads

@@ -41,7 +41,7 @@ class FlashTrittention(torch.autograd.Function):
                 convert_to_float32):
         _validate(Q, K1, K2, V1, V2)
         seq_len = Q.shape[2]
-        Q, K1, K2, V1, V2 = (t.contiguous() for t in (Q, K1, K2, V1, V2))
+        Q, K1, K2, V1, V2 = (_native.aligned(t) for t in (Q, K1, K2, V1, V2))
         k1_window, k2_window, kk_left, kk_right = process_masking_variables(
             seq_len, k1_window, k2_window, kk_left, kk_right)
         O = torch.empty_like(Q)
@@ -60,7 +60,7 @@ class FlashTrittention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dO):
         Q, K1, K2, V1, V2, O, lse = ctx.saved_tensors
-        dO = dO.contiguous()
+        dO = _native.aligned(dO)
         if dO.dtype != Q.dtype:
             dO = dO.to(Q.dtype)
         dq, dk1, dk2, dv1, dv2 = (torch.empty_like(Q) for _ in range(5))
