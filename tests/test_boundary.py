@@ -116,3 +116,16 @@ def test_package_surface_matches_reference_names():
     assert list(sig.parameters) == ["q", "k1", "k2", "v1", "v2", "softmax_scale", "kk_left", "kk_right",
                                     "k1_window", "k2_window", "causal", "convert_to_float32", "input_precision"]
     assert sig.parameters["kk_left"].default == 1 and sig.parameters["softmax_scale"].default == 1 / 8
+
+
+def test_aligned_copies_only_views_off_a_16_byte_boundary():
+    from flash_trittention import _native
+
+    buf = torch.arange(4 * 64 + 8, dtype=torch.float16)
+    on = buf[8:].view(4, 64)    # 16 bytes into the storage
+    off = buf[4:4 + 256].view(4, 64)  # 8 bytes into the storage
+    assert _native.aligned(on).data_ptr() == on.data_ptr()
+    fixed = _native.aligned(off)
+    assert fixed.data_ptr() != off.data_ptr() and fixed.data_ptr() % 16 == 0 and torch.equal(fixed, off)
+    strided = buf[:256].view(64, 4).t()
+    assert _native.aligned(strided).is_contiguous() and torch.equal(_native.aligned(strided), strided)
