@@ -109,6 +109,7 @@ size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype) {
     case TRITT_OP_TDP_BWD:
       a = simt_tdp_workspace(op, B, N, T, D, dtype);
       b = sm100_tdp_workspace(op, B, N, T, D, dtype);
+      if (op == TRITT_OP_TDP_FWD && b) b += sm100_tdp_fwd_optional_workspace(B, N, T, D, dtype);
       break;
     case TRITT_OP_DPS_FWD:
     case TRITT_OP_DPS_BWD:

@@ -124,6 +124,7 @@ int sm100_tdp_fwd(const TdpArgs& a);
 int sm100_tdp_bwd(const TdpArgs& a);
 size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype);
 size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D);
+size_t sm100_tdp_fwd_optional_workspace(int B, int N, int T, int D, int dtype);
 
 // Two-way soft-max attention forward on the tensor cores (16-bit operands [BN, T, D], head dimension 64 or 128):
 // out[r] = softmax_c(alpha x[r].k[c] + bias[c]) v[c] over the columns with (not causal, or c <= r <= c + win).

@@ -68,7 +68,11 @@ extern "C" int tritt_tdp_fwd_noalloc(const void* q, const void* k1, const void* 
                                      void* o, float* lse, int B, int N, int T, int D, int dtype, float alpha,
                                      int causal, int k1_window, int k2_window, int kk_left, int kk_right,
                                      int* status_word, int flags, tritt_stream_t stream) {
-  const size_t need = tritt_workspace_bytes(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
+  // (the bytes the forward cannot run without: the optional tail that tritt_workspace_bytes adds is used when the
+  //  scratch has room for it)
+  const size_t need_a = tritt::simt_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
+  const size_t need_b = tritt::sm100_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
+  const size_t need = need_a > need_b ? need_a : need_b;
   if (need > kNoAllocScratchBytes) {
     tritt::set_error(
         "tritt_tdp_fwd_noalloc: this problem needs %zu bytes of scratch, above the built-in maximum of %zu bytes "

@@ -63,7 +63,8 @@ template <int D> struct FwdCfg {
   static constexpr int kOffStats = kOffRing + kStages * kTileA;  // [2 parities][2 tiles][128][2] fp32: row (max, sum)
   static constexpr int kOffRed = kOffStats + 2 * 2 * 128 * 2 * 4;  // [2 tiles][4 warps][D] fp32 column sums
   static constexpr int kOffFstat = kOffRed + 2 * 4 * D * 4;        // [2 tiles][8] fp32 warp max / sum
-  static constexpr int kOffBars = kOffFstat + 2 * 8 * 4;
+  static constexpr int kOffNorm = kOffFstat + 2 * 8 * 4;            // [2 tiles][2 column halves][128] fp32: partial |A_row|^2
+  static constexpr int kOffBars = kOffNorm + 2 * 2 * 128 * 4;
   static constexpr int kSmem = kOffBars + 256;
   static constexpr int kTmemO = 256;  // S_a | S_b | acc_a | acc_b
 };
@@ -75,6 +76,8 @@ struct FwdParams {
   int T, BN, nq, q_mod, q_rem, causal, n_pairs;
   int k1w, k2w, kkl, kkr;  // windows of the causal mask (T or more = unbounded)
   float scale2;  // alpha * log2(e)
+  const float* k1_norm2_max;  // [BN] largest squared row norm of K1 per head, or null (no score bound available)
+  float bound_limit;          // rows whose score bound is below this skip the row-maximum pass
   int* status;
 };
 
@@ -351,6 +354,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     const int st = tid - 128;               // 0..255 over both warpgroups
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     float* stats = (float*)(smem + Cfg::kOffStats);
+    float* norms = (float*)(smem + Cfg::kOffNorm);
     uint32_t kt_count = 0, n = 0;
     bool alive = true;
     FT_DECL
@@ -361,6 +365,8 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       k_range(qa, qb, kt0, nkt);
       const int qx = x == 0 ? qa : qb;
       const T16* Qg = (const T16*)p.q + (size_t)bh * T * D;
+      // largest K1 row norm of this head: with |A_row| it bounds every score of the row (Cauchy-Schwarz)
+      const float k1_max = p.k1_norm2_max ? sqrtf(__ldg(p.k1_norm2_max + bh)) : INFINITY;
 
       for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
         int jt0, njt, ja, jb;
@@ -385,6 +391,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           const int r = st & 127;
           constexpr int CPT = D / 16;  // 16-byte chunks per thread
           const int c0 = (st >> 7) * CPT;
+          float na = 0.f, nb = 0.f;  // this thread's share of |A_a[r]|^2 and |A_b[r]|^2
 #pragma unroll
           for (int i = 0; i < CPT; ++i) {
             const int cc = c0 + i, hh = cc >> 3, c = cc & 7;
@@ -401,12 +408,19 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
               const float2 f = unpack2<T16>(w[e]);
               const float2 fa = unpack2<T16>(wa[e]), fb = unpack2<T16>(wb[e]);
               const float k0 = f.x * p.scale2, k1v = f.y * p.scale2;
-              oa[e] = pack2<T16>(k0 * fa.x, k1v * fa.y);
-              ob[e] = pack2<T16>(k0 * fb.x, k1v * fb.y);
+              const float a0 = k0 * fa.x, a1 = k1v * fa.y, b0 = k0 * fb.x, b1 = k1v * fb.y;
+              na = fmaf(a0, a0, fmaf(a1, a1, na));
+              nb = fmaf(b0, b0, fmaf(b1, b1, nb));
+              oa[e] = pack2<T16>(a0, a1);
+              ob[e] = pack2<T16>(b0, b1);
             }
             *reinterpret_cast<uint4*>(smem + Cfg::kOffAa + off) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
             *reinterpret_cast<uint4*>(smem + Cfg::kOffAb + off) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
           }
+          // (read by both tiles' owners of row r after their first s_ready wait of this k-tile, which this
+          //  thread's a_ready arrival below precedes; rewritten only after both have passed a_free)
+          norms[(0 * 2 + (st >> 7)) * 128 + r] = na;
+          norms[(1 * 2 + (st >> 7)) * 128 + r] = nb;
         }
         fence_async_smem();   // generic-proxy stores above -> visible to the tensor core's reads
         mbar_arrive(&bars.a_ready);
@@ -415,12 +429,22 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         // ---- walk over the slabs
         const uint32_t tS = tmem + lane_base + x * kBJ;
         float m_used = -INFINITY, l_sum = 0.f;
+        bool fast = false;
         for (int jt = 0; jt < njt; ++jt, ++n) {
           FT(0)
           alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x], n & 1, abort_flag));
           FT(3)
           if (!alive) break;
           tc_fence_after();
+          if (jt == 0) {
+            // Score bound of this row for the whole k-tile, |A_row| * max_j |K1_j| (log2 units).  Where it is
+            // small for every row of the warp, the bound itself serves as the soft-max reference: P stays
+            // within [2^-2b, 1], representable in the 16-bit type, so the row-maximum pass and every later
+            // rescaling are skipped.
+            const float bound = sqrtf(norms[(x * 2 + 0) * 128 + row] + norms[(x * 2 + 1) * 128 + row]) * k1_max;
+            fast = __all_sync(0xffffffffu, bound <= p.bound_limit);
+            if (fast) m_used = bound;
+          }
           if (jt == njt - 1) mbar_arrive(&bars.a_free);  // the last score product of this k-tile has read A_x
           // this row's valid columns within the slab: [lo, hi]; the warp takes the unmasked path when every
           // row sees the whole slab
@@ -433,6 +457,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 64 * nh - 1);
           // pass 1: row maximum
           float mx = -INFINITY;
+          if (!fast) {
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
             if (hf >= nh) break;
@@ -458,8 +483,11 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
                 if (c >= l2 && c <= h2) mx = fmaxf(mx, __uint_as_float(sr[c]));
             }
           }
+          }
           FT(4)
-          if (jt == 0) {
+          if (fast) {
+            // reference fixed for the k-tile
+          } else if (jt == 0) {
             m_used = mx;  // nothing accumulated yet in this k-tile
           } else {
             const bool grow = mx > m_used + kRescaleGap;
@@ -668,6 +696,24 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   if (tid == 0 && bars.abort_flag && p.status) atomicOr(p.status, 2);
 }
 
+// out[bh] = max_j |K1[bh, j, :]|^2 (fp32, compared as integers: non-negative floats order like their bit patterns);
+// a warp per row.  `out` must be zero on entry.
+template <typename T16>
+__global__ void k1_norm2_max_kernel(const T16* __restrict__ k1, float* __restrict__ out, size_t rows, int T, int D) {
+  const size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(k1 + r * D);
+  float s = 0.f;
+  for (int i = lane; i < D / 2; i += 32) {
+    const float2 f = unpack2<T16>(src[i]);
+    s = fmaf(f.x, f.x, fmaf(f.y, f.y, s));
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) atomicMax(reinterpret_cast<int*>(out + r / T), __float_as_int(s));
+}
+
 template <int D, typename T16>
 int launch_fwd(const TdpArgs& a) {
   using Cfg = FwdCfg<D>;
@@ -677,6 +723,17 @@ int launch_fwd(const TdpArgs& a) {
   silu_kernel<T16><<<(unsigned)((n / 8 + 255) / 256 + 1), 256, 0, a.stream>>>((const T16*)a.v1, sv1, n);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
+  // Optional tail of the workspace: per-head largest squared K1 row norm, for the kernel's score bound.
+  float* k1n = nullptr;
+  const size_t tail = align_up(n * 2, 256);
+  if (a.workspace_bytes >= tail + (size_t)BN * sizeof(float)) {
+    k1n = reinterpret_cast<float*>((char*)a.workspace + tail);
+    TRITT_CUDA_OK(cudaMemsetAsync(k1n, 0, (size_t)BN * sizeof(float), a.stream));
+    const size_t rows = (size_t)BN * a.T;
+    k1_norm2_max_kernel<T16><<<(unsigned)((rows + 7) / 8), 256, 0, a.stream>>>((const T16*)a.k1, k1n, rows, a.T, D);
+    count_launch();
+    TRITT_CUDA_OK(cudaGetLastError());
+  }
   CUtensorMap tmK1, tmK2, tmSV1;
   int rc;
   if ((rc = make_tmap_3d(&tmK1, a.k1, 2, D, a.T, BN, 64, 128))) return rc;
@@ -699,6 +756,9 @@ int launch_fwd(const TdpArgs& a) {
   p.kkl = a.mask.kkl;
   p.kkr = a.mask.kkr;
   p.scale2 = a.alpha * kLog2e;
+  p.k1_norm2_max = k1n;
+  // P = exp2(S - bound) lies in [2^-2 bound, 1]: normal numbers of the 16-bit type (bf16 2^-126, fp16 2^-14)
+  p.bound_limit = std::is_same<T16, __nv_bfloat16>::value ? 40.f : 6.f;
   p.status = a.status_word;
   if (p.nq == 0) return 0;
   auto kern = tdp_fwd_kernel<D, T16>;
@@ -727,6 +787,13 @@ bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m) {
   if (D != 64 && D != 128) return false;
   (void)m;  // every window of the causal mask is handled
   return T >= 1;
+}
+
+// Extra bytes behind the forward's SiLU(V1) copy that enable the score bound (the forward runs without them too).
+size_t sm100_tdp_fwd_optional_workspace(int B, int N, int T, int D, int dtype) {
+  if (dtype != TRITT_BF16 && dtype != TRITT_F16) return 0;
+  const size_t n = (size_t)B * N * T * D;
+  return align_up(n * 2, 256) - n * 2 + align_up((size_t)B * N * sizeof(float), 256);
 }
 
 size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype) {
