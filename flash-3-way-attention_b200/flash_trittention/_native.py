@@ -143,12 +143,14 @@ def dps_path(T, D, dtype, k_diff, flags=0) -> int:
     return lib().tritt_dps_path(T, D, dtype, int(k_diff), flags)
 
 
-def tdp_fwd(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr, q_mod=1, q_rem=0, flags=0):
+def tdp_fwd(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr, q_mod=1, q_rem=0, flags=0, ws=None):
+    """``ws``: a caller-provided workspace (uint8 tensor) instead of one of ``tritt_workspace_bytes`` bytes."""
     global launches
     B, N, T, D = q.shape
     dt = dtype_code(q.dtype)
     with torch.cuda.device(q.device):
-        ws = workspace(OP_TDP_FWD, B, N, T, D, dt, q.device)
+        if ws is None:
+            ws = workspace(OP_TDP_FWD, B, N, T, D, dt, q.device)
         rc = lib().tritt_tdp_fwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
                                  o.data_ptr(), lse.data_ptr(), B, N, T, D, dt, float(alpha), int(bool(causal)),
                                  _win(k1w, T), _win(k2w, T), _win(kkl, T), _win(kkr, T), q_mod, q_rem,

@@ -257,3 +257,26 @@ def test_windows_with_query_shards(windows):
     assert _native.read_status(torch.device(DEV)) == 0
     for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), [dq] + outs, full):
         assert float((a.float() - b.float()).abs().max()) <= 2e-2 * max(1.0, float(b.float().abs().max())), name
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_forward_with_and_without_the_score_bound(dtype):
+    """The forward takes the score bound |A_row| max|K1_j| as soft-max reference when the workspace has the tail for
+    the K1 row norms, and the two-pass row maximum when it has not: same result up to the rounding of P."""
+    B, N, T, D, alpha = 1, 2, 384, 128, 1.0 / 128
+    q, k1, k2, v1, v2, _ = orc.make_inputs(B, N, T, D, scale=0.5, seed=77, dtype=dtype)
+    t = [x.to(DEV) for x in (q, k1, k2, v1, v2)]
+    n = B * N * T * D
+    outs = []
+    for ws in (None, torch.empty(n * 2, dtype=torch.uint8, device=DEV)):
+        o, lse = torch.empty_like(t[0]), torch.empty(B, N, T, device=DEV)
+        _native.tdp_fwd(*t, o, lse, alpha, True, None, None, None, None, ws=ws)
+        torch.cuda.synchronize()
+        assert _native.read_status(torch.device(DEV)) == 0
+        outs.append((o.float(), lse))
+    assert float((outs[0][0] - outs[1][0]).abs().max()) <= 1e-2
+    assert float((outs[0][1] - outs[1][1]).abs().max()) <= 1e-3
+    z_ref, lse_ref = orc.tdp_forward(*[x.float() for x in (q, k1, k2, v1, v2)], alpha, True)
+    for o, lse in outs:
+        assert float((o.cpu() - z_ref).abs().max()) <= 2e-2
+        assert float((lse.cpu() - lse_ref).abs().max()) <= 2e-2
