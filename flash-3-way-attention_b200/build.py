@@ -20,12 +20,6 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "flash_trittention", "libtritt_sm100.so")
-# Development variant: TRITT_BUILD_DEFINES="-DTRITT_TIMING" builds a separate library with cycle counters.
-EXTRA = os.environ.get("TRITT_BUILD_DEFINES", "").split()
-if EXTRA:
-    _tag = os.environ.get("TRITT_BUILD_TAG", "dev")
-    OBJ = os.path.join(CSRC, "build_" + _tag)
-    LIB = os.path.join(HERE, "flash_trittention", f"libtritt_sm100_{_tag}.so")
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -51,7 +45,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
         if (not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(src), newest_hdr)):
             return obj, ""
-        cmd = [nvcc, *NVCC_FLAGS, *EXTRA, "-c", src, "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")

@@ -64,6 +64,25 @@ int check_ws(size_t need, void* ws, size_t have) {
   return 0;
 }
 
+// Windows are distances: the reference applies negative values literally (a negative k1 / k2 window or k_diff leaves
+// query rows without any attended pair, whose soft-max is undefined), so they are refused here instead.
+int check_windows(int causal, int a, int b, int c, int d) {
+  if (causal && (a < 0 || b < 0 || c < 0 || d < 0)) {
+    set_error("window arguments must be >= 0 (got %d, %d, %d, %d); pass T or more for an unlimited window", a, b, c, d);
+    return -10;
+  }
+  return 0;
+}
+
+// B*N is a grid dimension of the CUDA-core kernels.
+int check_heads(int B, int N) {
+  if ((long long)B * N > 65535) {
+    set_error("B*N = %lld exceeds the 65535 (batch*head) slices one call can take; split the batch", (long long)B * N);
+    return -11;
+  }
+  return 0;
+}
+
 int check_shard(int q_mod, int q_rem) {
   if (q_mod < 1 || q_rem < 0 || q_rem >= q_mod) {
     set_error("invalid query shard (q_mod=%d, q_rem=%d)", q_mod, q_rem);
@@ -113,7 +132,7 @@ size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype) {
       break;
     case TRITT_OP_DPS_FWD:
     case TRITT_OP_DPS_BWD:
-      a = simt_dps_workspace(op, B, N, T, D, dtype);
+      a = dps_workspace(op, B, N, T, D, dtype);
       break;
     default:
       return 0;
@@ -131,6 +150,8 @@ int tritt_tdp_fwd(const void* q, const void* k1, const void* k2, const void* v1,
   int rc = check_common(ptrs, 7, B, N, T, D, dtype);
   if (rc) return rc;
   if ((rc = check_shard(q_mod, q_rem))) return rc;
+  if ((rc = check_heads(B, N))) return rc;
+  if ((rc = check_windows(causal, k1_window, k2_window, kk_left, kk_right))) return rc;
   TdpArgs a{};
   a.q = q; a.k1 = k1; a.k2 = k2; a.v1 = v1; a.v2 = v2;
   a.out_o = o; a.out_lse = lse;
@@ -157,6 +178,8 @@ int tritt_tdp_bwd(const void* q, const void* k1, const void* k2, const void* v1,
   int rc = check_common(ptrs, 13, B, N, T, D, dtype);
   if (rc) return rc;
   if ((rc = check_shard(q_mod, q_rem))) return rc;
+  if ((rc = check_heads(B, N))) return rc;
+  if ((rc = check_windows(causal, k1_window, k2_window, kk_left, kk_right))) return rc;
   if (!partial && q_mod != 1) {
     set_error("a query-sharded backward yields partial key-side sums: pass TRITT_FLAG_BWD_PARTIAL");
     return -9;
@@ -186,7 +209,7 @@ int tritt_tdp_bwd_finalize(const void* v1, void* dk1, void* dk2, void* dv1, void
   return simt_tdp_bwd_finalize(v1, dk1, dk2, dv1, dv2, n, dtype, (const float*)workspace, (cudaStream_t)stream);
 }
 
-static int norm_kdiff(int k_diff, int T) { return (k_diff < 0 || k_diff > T) ? T : k_diff; }
+static int norm_kdiff(int k_diff, int T) { return k_diff > T ? T : k_diff; }
 
 int tritt_dps_fwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, void* o, float* m,
                   int B, int N, int T, int D, int dtype, float alpha, int causal, int k_diff, void* workspace,
@@ -194,14 +217,16 @@ int tritt_dps_fwd(const void* q, const void* k1, const void* k2, const void* v1,
   const void* ptrs[] = {q, k1, k2, v1, v2, o, m};
   int rc = check_common(ptrs, 7, B, N, T, D, dtype);
   if (rc) return rc;
-  if ((rc = check_ws(simt_dps_workspace(TRITT_OP_DPS_FWD, B, N, T, D, dtype), workspace, workspace_bytes))) return rc;
+  if ((rc = check_heads(B, N))) return rc;
+  if ((rc = check_windows(causal, k_diff, 0, 0, 0))) return rc;
+  if ((rc = check_ws(dps_workspace(TRITT_OP_DPS_FWD, B, N, T, D, dtype), workspace, workspace_bytes))) return rc;
   DpsArgs a{};
   a.q = q; a.k1 = k1; a.k2 = k2; a.v1 = v1; a.v2 = v2; a.out_o = o; a.out_m = m;
   a.B = B; a.N = N; a.T = T; a.D = D; a.dtype = dtype; a.alpha = alpha;
   a.causal = causal ? 1 : 0; a.k_diff = norm_kdiff(k_diff, T);
   a.workspace = workspace; a.workspace_bytes = workspace_bytes;
   a.status_word = status_word; a.flags = flags; a.stream = (cudaStream_t)stream;
-  return simt_dps_fwd(a);
+  return dps_fwd(a);
 }
 
 int tritt_dps_bwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, const void* o,
@@ -211,7 +236,9 @@ int tritt_dps_bwd(const void* q, const void* k1, const void* k2, const void* v1,
   const void* ptrs[] = {q, k1, k2, v1, v2, o, d_o, m, dq, dk1, dk2, dv1, dv2};
   int rc = check_common(ptrs, 13, B, N, T, D, dtype);
   if (rc) return rc;
-  if ((rc = check_ws(simt_dps_workspace(TRITT_OP_DPS_BWD, B, N, T, D, dtype), workspace, workspace_bytes))) return rc;
+  if ((rc = check_heads(B, N))) return rc;
+  if ((rc = check_windows(causal, k_diff, 0, 0, 0))) return rc;
+  if ((rc = check_ws(dps_workspace(TRITT_OP_DPS_BWD, B, N, T, D, dtype), workspace, workspace_bytes))) return rc;
   DpsArgs a{};
   a.q = q; a.k1 = k1; a.k2 = k2; a.v1 = v1; a.v2 = v2; a.o = o; a.d_o = d_o; a.m_in = m;
   a.dq = dq; a.dk1 = dk1; a.dk2 = dk2; a.dv1 = dv1; a.dv2 = dv2;
@@ -219,7 +246,7 @@ int tritt_dps_bwd(const void* q, const void* k1, const void* k2, const void* v1,
   a.causal = causal ? 1 : 0; a.k_diff = norm_kdiff(k_diff, T);
   a.workspace = workspace; a.workspace_bytes = workspace_bytes;
   a.status_word = status_word; a.flags = flags; a.stream = (cudaStream_t)stream;
-  return simt_dps_bwd(a);
+  return dps_bwd(a);
 }
 
 }  // extern "C"

@@ -56,12 +56,21 @@ inline size_t dtype_size(int dtype) { return dtype == TRITT_F32 ? 4 : 2; }
 // trittention_pytorch.py:68-75): (q, j, k) is attended iff
 //   j <= q <= j + k1w,  k <= q <= k + k2w,  k - kkl <= j <= k + kkr     (causal)
 // and always when not causal.  Windows are normalised on the host so that
-// "unlimited" equals T.
+// "unlimited" (anything >= T) equals T; negative windows are refused at the entry points.
 struct TdpMask {
   int causal, T, k1w, k2w, kkl, kkr;
   __host__ __device__ bool valid(int q, int j, int k) const {
     if (!causal) return true;
     return j <= q && q - j <= k1w && k <= q && q - k <= k2w && k - j <= kkl && j - k <= kkr;
+  }
+  // Query q attends the single pair (q, q) (or, not causal, T == 1).  Its soft-max is then the constant 1 and the
+  // gradient of its scores is exactly zero; the backward kernels use that instead of forming P (dP - Dq), whose two
+  // terms agree only up to the 16-bit rounding of the stored output when P = 1.
+  // (Another pair exists iff one of (q-1, q), (q, q-1), (q-1, q-1) is attended.)
+  __host__ __device__ bool single_pair(int q) const {
+    if (!causal) return T == 1;
+    if (q == 0) return true;
+    return !((k1w >= 1 && kkl >= 1) || (k2w >= 1 && kkr >= 1) || (k1w >= 1 && k2w >= 1));
   }
   // full windows: the mask is the plain "j <= q and k <= q" wedge
   __host__ __device__ bool full_windows() const {
@@ -70,7 +79,7 @@ struct TdpMask {
 };
 
 inline TdpMask make_tdp_mask(int causal, int T, int k1w, int k2w, int kkl, int kkr) {
-  auto norm = [T](int w) { return (w < 0 || w > T) ? T : w; };
+  auto norm = [T](int w) { return w > T ? T : (w < 0 ? 0 : w); };
   return TdpMask{causal ? 1 : 0, T, norm(k1w), norm(k2w), norm(kkl), norm(kkr)};
 }
 
@@ -115,9 +124,9 @@ int simt_tdp_bwd_finalize(const void* v1, void* dk1, void* dk2, void* dv1, void*
                           const float* partials, cudaStream_t stream);
 size_t simt_tdp_workspace(int op, int B, int N, int T, int D, int dtype);
 
-int simt_dps_fwd(const DpsArgs& a);
-int simt_dps_bwd(const DpsArgs& a);
-size_t simt_dps_workspace(int op, int B, int N, int T, int D, int dtype);
+int dps_fwd(const DpsArgs& a);
+int dps_bwd(const DpsArgs& a);
+size_t dps_workspace(int op, int B, int N, int T, int D, int dtype);
 
 bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m);
 int sm100_tdp_fwd(const TdpArgs& a);

@@ -9,15 +9,22 @@
 //
 // The scratch therefore lives in a fixed array in this library's device image.  Consequences a user
 // must know:
-//   * every GPU whose context loads the library holds kNoAllocScratchBytes (8 MiB) until the process
-//     exits, whether or not this entry point is ever called;
-//   * problems whose scratch does not fit (16-bit inputs with B*N*T*D > 4 194 304 elements) are
-//     rejected with an error; fp32 inputs need no scratch and are not limited;
+//   * every GPU whose context has loaded this library's device image holds kNoAllocScratchBytes (8 MiB)
+//     from then until the process exits.  With CUDA's default lazy module loading the driver may load
+//     the image only at the first call that needs it, and that load reserves device memory inside the
+//     driver: "allocates nothing" means that this entry point calls no allocation routine of the CUDA
+//     runtime or of any library, not that the driver never touches device memory on its behalf;
+//   * problems whose scratch does not fit are rejected with an error: 16-bit inputs on the
+//     tensor-core path (head dimension 64 or 128) with B*N*T*D > 4 194 304 elements.  Calls that run on
+//     the CUDA-core path (fp32 inputs, other head dimensions, TRITT_FLAG_FORCE_SIMT) need no scratch and
+//     are not limited;
 //   * all calls on one GPU share the one array.  Nothing in it has to start at zero (each call
 //     rewrites the part it reads), but two calls that overlap in time on the same GPU - different
 //     streams or different host threads - race on it and produce garbage.  Serialise them;
 //   * the first call on each device looks up the array's device address; make that first call
-//     before starting any stream capture on that device.
+//     before starting any stream capture on that device.  The address is cached per device ordinal
+//     and does not survive cudaDeviceReset or the destruction of the device's primary context: a
+//     process that does either must not call this entry point afterwards.
 #include "tritt_common.cuh"
 
 #include <mutex>
@@ -68,15 +75,17 @@ extern "C" int tritt_tdp_fwd_noalloc(const void* q, const void* k1, const void* 
                                      void* o, float* lse, int B, int N, int T, int D, int dtype, float alpha,
                                      int causal, int k1_window, int k2_window, int kk_left, int kk_right,
                                      int* status_word, int flags, tritt_stream_t stream) {
-  // (the bytes the forward cannot run without: the optional tail that tritt_workspace_bytes adds is used when the
-  //  scratch has room for it)
-  const size_t need_a = tritt::simt_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
-  const size_t need_b = tritt::sm100_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
-  const size_t need = need_a > need_b ? need_a : need_b;
+  // The bytes the kernel family this call will run on cannot do without (the same choice tritt_tdp_fwd makes; the
+  // optional tail that tritt_workspace_bytes adds is used when the scratch has room for it).
+  const bool tc = tritt_tdp_path(TRITT_OP_TDP_FWD, T, D, dtype, causal, k1_window, k2_window, kk_left, kk_right,
+                                 flags) == TRITT_PATH_TCGEN05;
+  const size_t need = tc ? tritt::sm100_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype)
+                         : tritt::simt_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
   if (need > kNoAllocScratchBytes) {
     tritt::set_error(
         "tritt_tdp_fwd_noalloc: this problem needs %zu bytes of scratch, above the built-in maximum of %zu bytes "
-        "(16-bit inputs are limited to B*N*T*D <= %zu elements); use tritt_tdp_fwd with a caller-provided workspace",
+        "(16-bit inputs on the tensor-core path are limited to B*N*T*D <= %zu elements); use tritt_tdp_fwd with a "
+        "caller-provided workspace",
         need, kNoAllocScratchBytes, kNoAllocScratchBytes / 2);
     return -42;
   }

@@ -3,7 +3,7 @@
 // backward) or one column (column-owner backward); each lane keeps a quarter of the head dimension of
 // every per-owner vector in registers, dot products are finished with two shuffles inside the quad, and
 // the tiles of the other axis are staged in shared memory and read with broadcast 16-byte loads.
-// Included by tritt_simt_dps.cu after AttnParams / load_src / attn_valid are defined.
+// Included by tritt_simt_dps.cuh after AttnParams / load_src / attn_valid are defined.
 #pragma once
 
 constexpr int kQuadOwners = 32;   // owners per CTA (128 threads)

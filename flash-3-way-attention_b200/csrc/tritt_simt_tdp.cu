@@ -91,6 +91,7 @@ __global__ void tdp_simt_kernel(SimtTdpParams p) {
   __syncthreads();
 
   const TdpMask mk = p.mask;
+  const bool single = mk.single_pair(q);         // one attended pair: the score gradient is exactly zero
   const int xw = p.role == 0 ? mk.k2w : mk.k1w;  // window of the row axis against q
   const int cw = p.role == 0 ? mk.k1w : mk.k2w;
   // band of the column axis around a row index x: c in [x - below, x + above]
@@ -167,7 +168,7 @@ __global__ void tdp_simt_kernel(SimtTdpParams p) {
           } else {
             float dp = 0.f;
             for (int h = 0; h < D; ++h) dp = fmaf(VEC(1, h), tV[cc * D + h], dp);
-            const float ds = pr * (dp - Dq);
+            const float ds = single ? 0.f : pr * (dp - Dq);
             for (int h = 0; h < D; ++h) {
               VEC(2, h) = fmaf(ds, tK[cc * D + h], VEC(2, h));
               VEC(3, h) = fmaf(pr, tV[cc * D + h], VEC(3, h));

@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
   __syncthreads();
 
   const TdpMask mk = p.mask;
+  const bool single = mk.single_pair(q);         // one attended pair: the score gradient is exactly zero
   const int xw = p.role == 0 ? mk.k2w : mk.k1w;  // window of the row axis against q
   const int cw = p.role == 0 ? mk.k1w : mk.k2w;
   // band of the column axis around a row index x: c in [x - below, x + above]
@@ -216,7 +217,7 @@ __global__ void __launch_bounds__(128) tdp_simt_quad_kernel(SimtTdpParams p) {
               d3 = fmaf(ay[4 * i + 3], vv.w, d3);
             }
             const float dp = tdp_row_sum<LPR>((d0 + d1) + (d2 + d3));
-            ds = pr * (dp - Dq);
+            ds = single ? 0.f : pr * (dp - Dq);
           }
 #pragma unroll
           for (int i = 0; i < DQ / 4; ++i) {

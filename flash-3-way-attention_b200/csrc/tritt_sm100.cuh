@@ -49,17 +49,21 @@ constexpr long long kWaitTicks = 2000000000LL;
 // Bounded wait.  `abort_flag` is a CTA-shared word that any thread sets when its wait ran
 // out; once set, every later wait returns false immediately so that all warps fall through
 // to the kernel's teardown.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                long long limit_ticks) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitTicks) {
+    if (clock64() - t0 > limit_ticks) {
       *abort_flag = 1;
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limit(bar, parity, abort_flag, kWaitTicks);
 }
 
 // ------------------------------------------------------------------ fences

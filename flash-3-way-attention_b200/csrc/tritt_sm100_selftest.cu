@@ -12,62 +12,6 @@
 namespace tritt {
 
 namespace {
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeFn encode_fn() {
-  static EncodeFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
-    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !p) return nullptr;
-    fn = (EncodeFn)p;
-  }
-  return fn;
-}
-int encode_3d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, CUtensorMapSwizzle swz, const void* base,
-              uint64_t cols, uint64_t rows, uint64_t bn, uint32_t box_cols, uint32_t box_rows) {
-  EncodeFn fn = encode_fn();
-  if (!fn) {
-    set_error("cuTensorMapEncodeTiled is not available from the driver");
-    return -20;
-  }
-  cuuint64_t dims[3] = {cols, rows, bn};
-  cuuint64_t strides[2] = {cols * elem_bytes, rows * cols * elem_bytes};
-  cuuint32_t box[3] = {box_cols, box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled failed with CUresult %d (cols=%llu rows=%llu bn=%llu)", (int)r,
-              (unsigned long long)cols, (unsigned long long)rows, (unsigned long long)bn);
-    return -22;
-  }
-  return 0;
-}
-}  // namespace
-
-int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t cols, uint64_t rows, uint64_t bn,
-                 uint32_t box_cols, uint32_t box_rows) {
-  if (elem_bytes != 2) {
-    set_error("make_tmap_3d is for 16-bit elements");
-    return -21;
-  }
-  return encode_3d(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, CU_TENSOR_MAP_SWIZZLE_128B, base, cols, rows, bn, box_cols,
-                   box_rows);
-}
-
-int make_tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t bn,
-                     uint32_t box_cols, uint32_t box_rows) {
-  // box rows are box_cols * 4 bytes wide: 64 bytes -> 64-byte swizzle, 128 bytes -> 128-byte swizzle
-  const CUtensorMapSwizzle swz = box_cols * 4 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                 : box_cols * 4 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
-                                                      : CU_TENSOR_MAP_SWIZZLE_NONE;
-  return encode_3d(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, swz, base, cols, rows, bn, box_cols, box_rows);
-}
-
-namespace {
 using namespace sm100;
 
 template <bool BF16>
@@ -171,8 +115,53 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   if (warp == 0) tmem_dealloc(tbase, 512);
 }
 
+// Exercises the time-out path every tensor-core kernel shares: one thread is meant to arrive on an mbarrier, a
+// warp waits for it with the bounded wait.  With `skip_arrival` the arrival never happens, the wait gives up after
+// `limit_ticks` clock ticks, the CTA records status bit 128, releases its tensor memory and returns normally.
+__global__ void __launch_bounds__(64, 1) wait_expiry_kernel(int skip_arrival, long long limit_ticks, int* status) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 32);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  bool ok = true;
+  if (warp == 0) {
+    if (tid == 0 && !skip_arrival) mbar_arrive(&bar);
+  } else {
+    ok = __all_sync(0xffffffffu, mbar_wait_limit(&bar, 0, &abort_flag, limit_ticks));
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base_s, 32);
+  if (tid == 32 && !ok && status) atomicOr(status, 128);
+}
+
 }  // namespace
 }  // namespace tritt
+
+extern "C" int tritt_selftest_wait_expiry(int skip_arrival, long long limit_ticks, int* status_word,
+                                          tritt_stream_t stream) {
+  using namespace tritt;
+  if (limit_ticks < 1 || limit_ticks > sm100::kWaitTicks) {
+    set_error("limit_ticks must lie in [1, %lld]", sm100::kWaitTicks);
+    return -1;
+  }
+  wait_expiry_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(skip_arrival, limit_ticks, status_word);
+  count_launch();
+  TRITT_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int tritt_selftest_umma(const void* A, const void* Bm, const void* V, float* C, float* C2, int dtype,
                                    int* status_word, tritt_stream_t stream) {

@@ -24,33 +24,6 @@ template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
   return __half22float2(*reinterpret_cast<__half2*>(&v));
 }
 
-// exp2 on the FMA pipe, for x <= 0 (probabilities): x is split into a rounded integer part (moved into
-// the exponent bits) and a fraction f in [-0.5, 0.5] whose power of two is a degree-4 polynomial
-// (relative error < 5e-5, far below the 16-bit rounding of P).  Used for a share of the exponentials so
-// that the special-function unit (16 exp2 per clock per SM) stops being the bound of the soft-max.
-__device__ __forceinline__ float exp2_fma(float x) {
-  x = fmaxf(x, -126.f);
-  const float magic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
-  const float t = x + magic;
-  const float f = x - (t - magic);
-  float pl = 0.009618129f;
-  pl = fmaf(pl, f, 0.05550411f);
-  pl = fmaf(pl, f, 0.2402265f);
-  pl = fmaf(pl, f, 0.6931472f);
-  pl = fmaf(pl, f, 1.0f);
-  return __int_as_float(__float_as_int(pl) + (__float_as_int(t) << 23));
-}
-// every EMU-th element goes to the FMA pipe (EMU = 0: none).  Measured at B=1, N=16, T=2048, D=128: any share
-// made both kernels slower (forward 26.0 -> 28.7 ms at 1/4, backward 103.7 -> 107.8 ms at 1/3): the soft-max
-// warps are bound by issue slots and latency, not by the special-function unit, so the default is 0.
-template <int EMU>
-__device__ __forceinline__ float exp2_mix(float x, int idx) {
-  if constexpr (EMU > 0) {
-    if ((idx % EMU) == EMU - 1) return exp2_fma(x);
-  }
-  return exp2f(x);
-}
-
 // Sum of v[0..31] over the 32 lanes of a warp, column-wise: on return lane i holds the
 // total of column i.  31 shuffles instead of 32 full reductions.
 __device__ __forceinline__ float warp_transpose_sum(float (&v)[32], int lane) {

@@ -38,17 +38,10 @@
 #include <type_traits>
 
 namespace tritt {
-#ifdef TRITT_TIMING
-__device__ long long g_timing[148 * 16];
-#endif
 namespace {
 using namespace sm100;
 
 constexpr int kBC = 128;  // key columns per slab
-#ifndef TRITT_EMU_BWD
-#define TRITT_EMU_BWD 0
-#endif
-constexpr int kEmuBwd = TRITT_EMU_BWD;  // every kEmuBwd-th exponential runs on the FMA pipe (0 = none)
 
 template <int D> struct BwdCfg {
   static constexpr int kTileA = 128 * D * 2;   // one 128-row operand / key / value tile
@@ -95,15 +88,6 @@ struct BwdBarriers {
   int abort_flag;
 };
 
-#ifdef TRITT_TIMING
-#define TT_DECL long long tt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tt_t = clock64();
-#define TT(slot) { const long long tt_n = clock64(); tt_acc[slot] += tt_n - tt_t; tt_t = tt_n; }
-#define TT_FLUSH(basei) if (blockIdx.x < 148) { for (int i = 0; i < 8; ++i) g_timing[blockIdx.x * 16 + (basei) + i] = tt_acc[i]; }
-#else
-#define TT_DECL
-#define TT(slot)
-#define TT_FLUSH(basei)
-#endif
 
 template <int D, typename T16, int NSW>
 __global__ void __launch_bounds__(BwdThreads<NSW>::kTotal, 1)
@@ -265,12 +249,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), 16384);  // row-major (MN-major) view
       uint32_t xt_count = 0, base = 0, n = 0;
       bool alive = true;
-      TT_DECL
       auto wait_full = [&](uint32_t pos) {
-        TT(0)
-        const bool ok = mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
-        TT(1)
-        return ok;
+        return mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
       };
       // One 8-instruction accumulation chain each (D = 128): S = A Kc^T, dP = A' Vc^T (operands in shared
       // memory, key/value tile K-major), U (+)= P Vc, G (+)= dS Kc (P / dS from tensor memory, the tile row-major).
@@ -283,7 +263,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           mma_ss_lo(tmem + Cfg::kTmemS, aLo + kk, bLo + kk, kHi, idesc_s, k > 0);
         }
         mma_commit(&bars.s_ready);
-        TT(4)
         return true;
       };
       auto issue_dp = [&](uint32_t pos) -> bool {
@@ -295,7 +274,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           mma_ss_lo(tmem + Cfg::kTmemDP, a2Lo + kk, bLo + kk, kHi, idesc_s, k > 0);
         }
         mma_commit(&bars.dp_ready);
-        TT(5)
         return true;
       };
       // soft-max warpgroup g packed its CW columns of P into S[CW*g, CW*g + CW/2) and of dS into dP[CW*g, ...)
@@ -313,7 +291,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           first = false;
         }
         if (half == 1) mma_commit(&bars.ring_empty[st]);
-        TT(6)
       };
       auto issue_g = [&](uint32_t pos, uint32_t acc) {
         const uint32_t st = pos % NS;
@@ -323,7 +300,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           mma_ts_lo(tmem + Cfg::kTmemG, a, ringMN + st * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
         }
         mma_commit(&bars.ring_empty[st]);
-        TT(6)
       };
 
       for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
@@ -334,35 +310,27 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
           int c0, ncs;
           c_range(q, win, xt, c0, ncs);
-          TT(0)
           if (!mbar_wait(&bars.a_ready, xt_count & 1, abort_flag)) { alive = false; break; }
-          TT(2)
           tc_fence_after();
           if (!issue_s(base) || !issue_dp(base + 1)) { alive = false; break; }
           for (int c = 0; c < ncs && alive; ++c, ++n) {
             const bool more = c + 1 < ncs;
-            TT(0)
             if (!mbar_wait(&bars.p_ready[0], n & 1, abort_flag)) { alive = false; break; }
             if (c == 0) {
               // the fold warpgroup must have drained the previous tile's U
               if (!mbar_wait(&bars.u_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
             }
-            TT(3)
             tc_fence_after();
             issue_u_half(base + 2 * c + 1, c > 0, 0);
-            TT(0)
             if (!mbar_wait(&bars.p_ready[1], n & 1, abort_flag)) { alive = false; break; }
-            TT(3)
             tc_fence_after();
             issue_u_half(base + 2 * c + 1, c > 0, 1);
             if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
-            TT(0)
             if (!mbar_wait(&bars.ds_ready, n & 1, abort_flag)) { alive = false; break; }
             if (c == 0) {
               // ... and the previous tile's G
               if (!mbar_wait(&bars.g_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
             }
-            TT(3)
             tc_fence_after();
             issue_g(base + 2 * c, c > 0);
             if (more && !issue_dp(base + 2 * (c + 1) + 1)) { alive = false; break; }
@@ -371,8 +339,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           base += 2 * ncs;
         }
       }
-      TT(0)
-      TT_FLUSH(0)
     }
   } else if (warp >= 4 && warp < kFoldWarp0) {
     // ------------------------------------------------------------------ soft-max warpgroups
@@ -384,7 +350,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     float* misc = (float*)(smem + Cfg::kOffMisc);
     uint32_t xt_count = 0, n = 0, sync_phase = 0, item_count = 0;
     bool alive = true;
-    TT_DECL
     auto sm_sync = [&]() -> bool {
       mbar_arrive(&bars.sm_sync);
       const bool ok = mbar_wait(&bars.sm_sync, sync_phase & 1, abort_flag);
@@ -420,6 +385,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       }
       if (!sm_sync()) { alive = false; break; }
       const float Dq = misc[0] + misc[1] + misc[2] + misc[3];
+      // a query that attends a single pair has P = 1 and a score gradient of exactly zero (TdpMask::single_pair)
+      const bool single = TdpMask{p.causal, T, p.k1w, p.k2w, p.kkl, p.kkr}.single_pair(q);
       const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e;
       const float scale2 = p.alpha * kLog2e;
 
@@ -427,9 +394,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         int c0, ncs;
         c_range(q, win, xt, c0, ncs);
         // ---- operand formation (in place): A = scale2*Q[q] (.) X tile,  A' = dO[q] (.) Y tile
-        TT(0)
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.xy_full, xt_count & 1, abort_flag));
-        TT(1)
         if (!alive) break;
 #pragma unroll
         for (int ci = 0; ci < D / 8 / NSW; ++ci) {
@@ -466,9 +431,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           const int lo = c_lo - (c0 + c) * kBC - wg * CW, hi = c_hi - (c0 + c) * kBC - wg * CW;
           uint32_t pk[CW / 2];
           // ---- S -> P
-          TT(2)
           alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready, n & 1, abort_flag));
-          TT(3)
           if (!alive) break;
           tc_fence_after();
           static_assert(CW == 64, "the two-half hand-off of P is written for two soft-max warpgroups");
@@ -481,8 +444,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             if (l2 <= 0 && h2 >= 31) {
 #pragma unroll
               for (int i = 0; i < 32; i += 2)
-                pk[hf * 16 + (i >> 1)] = pack2<T16>(exp2_mix<kEmuBwd>(__uint_as_float(s[i]) - lse2, i),
-                                                    exp2_mix<kEmuBwd>(__uint_as_float(s[i + 1]) - lse2, i + 1));
+                pk[hf * 16 + (i >> 1)] = pack2<T16>(exp2f(__uint_as_float(s[i]) - lse2),
+                                                    exp2f(__uint_as_float(s[i + 1]) - lse2));
             } else {
 #pragma unroll
               for (int i = 0; i < 32; i += 2) {
@@ -496,12 +459,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars.p_ready[hf]);
-            TT(4 + hf)
           }
           // ---- dP, P -> dS
-          TT(2)
           alive = __all_sync(0xffffffffu, mbar_wait(&bars.dp_ready, n & 1, abort_flag));
-          TT(3)
           if (!alive) break;
           tc_fence_after();
           if (c == ncs - 1) {
@@ -514,13 +474,16 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 #pragma unroll
             for (int sc = 0; sc < CW / 32; ++sc) tmem_ld32(tDP + sc * 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[sc * 32]));
             tmem_wait_ld();
-            TT(6)
+            if (single) {
 #pragma unroll
-            for (int i = 0; i < CW; i += 2) {
-              const float2 pp = unpack2<T16>(pk[i >> 1]);
-              dk[i >> 1] = pack2<T16>(pp.x * (__uint_as_float(dp[i]) - Dq), pp.y * (__uint_as_float(dp[i + 1]) - Dq));
+              for (int i = 0; i < CW / 2; ++i) dk[i] = 0u;
+            } else {
+#pragma unroll
+              for (int i = 0; i < CW; i += 2) {
+                const float2 pp = unpack2<T16>(pk[i >> 1]);
+                dk[i >> 1] = pack2<T16>(pp.x * (__uint_as_float(dp[i]) - Dq), pp.y * (__uint_as_float(dp[i + 1]) - Dq));
+              }
             }
-            TT(7)
           }
           tmem_st(tDP, dk);  // dS -> first half of this warpgroup's dP columns
           tmem_wait_st();
@@ -530,7 +493,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         if (!alive) break;
       }
     }
-    if (wg == 0 && row == 0) { TT_FLUSH(8) }
   } else if (warp >= kFoldWarp0) {
     // ------------------------------------------------------------------ fold warpgroup
     // Drains G / U of a finished tile: 32-column pieces -> registers -> scaled by Q[q] / dO[q] -> shared memory
@@ -715,13 +677,6 @@ int launch_bwd_any(const TdpArgs& a) {
 
 }  // namespace
 
-#ifdef TRITT_TIMING
-}  // namespace tritt
-extern "C" int tritt_debug_read_timing(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, tritt::g_timing, sizeof(long long) * 148 * 16);
-}
-namespace tritt {
-#endif
 
 size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D) {
   const size_t n = (size_t)B * N * T * D;

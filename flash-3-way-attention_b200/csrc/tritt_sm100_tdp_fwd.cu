@@ -32,26 +32,11 @@
 #include <type_traits>
 
 namespace tritt {
-#ifdef TRITT_TIMING
-// Development build only: per-CTA cycle counters of where each role waits.
-__device__ long long g_timing_fwd[148 * 16];
-#define FT_DECL long long tt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tt_t = clock64();
-#define FT(slot) { const long long tt_n = clock64(); tt_acc[slot] += tt_n - tt_t; tt_t = tt_n; }
-#define FT_FLUSH(basei) if (blockIdx.x < 148) { for (int i = 0; i < 8; ++i) g_timing_fwd[blockIdx.x * 16 + (basei) + i] = tt_acc[i]; }
-#else
-#define FT_DECL
-#define FT(slot)
-#define FT_FLUSH(basei)
-#endif
 namespace {
 using namespace sm100;
 
 constexpr int kThreads = 512;
 constexpr int kBJ = 128;            // key columns per slab
-#ifndef TRITT_EMU_FWD
-#define TRITT_EMU_FWD 0
-#endif
-constexpr int kEmuFwd = TRITT_EMU_FWD;  // every kEmuFwd-th exponential runs on the FMA pipe (0 = none)
 constexpr float kRescaleGap = 8.f;  // rescale the accumulator only when the row max grew by more than 2^8
 
 template <int D> struct FwdCfg {
@@ -249,12 +234,8 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), 16384);  // row-major (MN-major) view
       uint32_t kt_count = 0, base = 0, n = 0;  // n: slabs finished so far (same for both tiles)
       bool alive = true;
-      FT_DECL
       auto wait_full = [&](uint32_t pos) {
-        FT(0)
-        const bool ok = mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
-        FT(1)
-        return ok;
+        return mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
       };
       auto release = [&](uint32_t pos) { mma_commit(&bars.ring_empty[pos % NS]); };
       // S_x = A_x * K1tile^T  (one chain of D/16 instructions); hm != 0: only 64 rows of the key tile (the lower
@@ -303,9 +284,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
           int jt0, njt;
           j_range(qa, qb, kt, jt0, njt);
-          FT(0)
           if (!mbar_wait(&bars.a_ready, kt_count & 1, abort_flag)) { alive = false; break; }
-          FT(2)
           tc_fence_after();
           if (!wait_full(base)) { alive = false; break; }
           int ja, jb;
@@ -319,13 +298,10 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             const bool more = jt + 1 < njt;
             const int hm_next = more ? halves(ja, jb, (jt0 + jt + 1) * kBJ) : 0;
             for (int x = 0; x < 2 && alive; ++x) {
-              FT(0)
               if (!mbar_wait(&bars.p_ready[x], n & 1, abort_flag)) { alive = false; break; }
-              FT(3)
               if (jt == 0) {
                 // the fold warpgroup must have drained the previous k-tile's accumulator of this tile
                 if (!mbar_wait(&bars.o_free[x], (kt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
-                FT(4)
               }
               tc_fence_after();
               if (x == 0 && !wait_full(pv)) { alive = false; break; }
@@ -343,8 +319,6 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           base += 2 * njt;
         }
       }
-      FT(0)
-      FT_FLUSH(0)
     }
   } else if (warp >= 4 && warp < 12) {
     // ------------------------------------------------------------------ soft-max warpgroups
@@ -357,7 +331,6 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     float* norms = (float*)(smem + Cfg::kOffNorm);
     uint32_t kt_count = 0, n = 0;
     bool alive = true;
-    FT_DECL
 
     for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
       int bh, qa, qb, kt0, nkt;
@@ -383,9 +356,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           c_hi = in_k ? min(qx, k_r + p.kkr) : qx;
         }
         // ---- operand formation: A_a = s*Q[qa] (.) K2tile (in place), A_b = s*Q[qb] (.) K2tile
-        FT(0)
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.k2_full, kt_count & 1, abort_flag));
-        FT(1)
         if (!alive) break;
         {
           const int r = st & 127;
@@ -424,16 +395,13 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         }
         fence_async_smem();   // generic-proxy stores above -> visible to the tensor core's reads
         mbar_arrive(&bars.a_ready);
-        FT(2)
 
         // ---- walk over the slabs
         const uint32_t tS = tmem + lane_base + x * kBJ;
         float m_used = -INFINITY, l_sum = 0.f;
         bool fast = false;
         for (int jt = 0; jt < njt; ++jt, ++n) {
-          FT(0)
           alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x], n & 1, abort_flag));
-          FT(3)
           if (!alive) break;
           tc_fence_after();
           if (jt == 0) {
@@ -484,7 +452,6 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             }
           }
           }
-          FT(4)
           if (fast) {
             // reference fixed for the k-tile
           } else if (jt == 0) {
@@ -525,8 +492,8 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
               float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
               for (int c = 0; c < 64; c += 2) {
-                const float p0 = exp2_mix<kEmuFwd>(__uint_as_float(sr[c]) - m_used, c);
-                const float p1 = exp2_mix<kEmuFwd>(__uint_as_float(sr[c + 1]) - m_used, c + 1);
+                const float p0 = exp2f(__uint_as_float(sr[c]) - m_used);
+                const float p1 = exp2f(__uint_as_float(sr[c + 1]) - m_used);
                 ps0 += p0;
                 ps1 += p1;
                 pk[c >> 1] = pack2<T16>(p0, p1);
@@ -546,11 +513,9 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             tmem_st32(tS + hf * 32, pk);
           }
           l_sum += psum;
-          FT(5)
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(&bars.p_ready[x]);
-          FT(6)
         }
         if (!alive) break;
         // ---- hand this k-tile's row statistics to the fold warpgroup
@@ -563,7 +528,6 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       }
       if (!alive) break;
     }
-    if (x == 0 && row == 0) { FT_FLUSH(8) }
   } else if (warp >= 12) {
     // ------------------------------------------------------------------ fold warpgroup
     // After the last P*V of a k-tile: O[q_x,h] accumulates sum_r w_r acc_x[r,h] V2[k_r,h] with
@@ -773,13 +737,6 @@ int launch_fwd(const TdpArgs& a) {
 
 }  // namespace
 
-#ifdef TRITT_TIMING
-}  // namespace tritt
-extern "C" int tritt_debug_read_timing_fwd(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, tritt::g_timing_fwd, sizeof(long long) * 148 * 16);
-}
-namespace tritt {
-#endif
 
 bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m) {
   if (op != TRITT_OP_TDP_FWD && op != TRITT_OP_TDP_BWD) return false;

@@ -13,6 +13,8 @@ _LAZY_ATTRS = {
     "flash_trittention": (".triple_dot_product.flash_trittention", "flash_trittention"),
     "TrittentionTriton": (".dot_product_sum.trittention_triton", "TrittentionTriton"),
     "TrittentionTDP": (".ops", "TrittentionTDP"),  # torch.library operators + module (not in the reference)
+    # raises if a kernel of an earlier call gave up on a bounded barrier wait (not in the reference)
+    "check_status": ("._native", "check_status"),
 }
 
 

@@ -12,7 +12,7 @@ import threading
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, os.environ.get("TRITT_LIB", "libtritt_sm100.so"))
+LIB_PATH = os.path.join(_HERE, "libtritt_sm100.so")
 
 F32, F16, BF16 = 0, 1, 2
 OP_TDP_FWD, OP_TDP_BWD, OP_DPS_FWD, OP_DPS_BWD = 0, 1, 2, 3
@@ -25,12 +25,13 @@ _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 SYMBOLS = (
     "tritt_version", "tritt_kernel_launches", "tritt_last_error", "tritt_workspace_bytes", "tritt_tdp_path", "tritt_dps_path", "tritt_tdp_fwd",
     "tritt_tdp_bwd", "tritt_tdp_bwd_finalize", "tritt_tdp_bwd_partials_offset", "tritt_dps_fwd",
-    "tritt_dps_bwd", "tritt_selftest_umma", "tritt_tdp_fwd_noalloc", "tritt_noalloc_scratch_bytes",
+    "tritt_dps_bwd", "tritt_selftest_umma", "tritt_selftest_wait_expiry", "tritt_tdp_fwd_noalloc",
+    "tritt_noalloc_scratch_bytes",
 )
 
 _lib = None
 _lock = threading.Lock()
-_status = {}
+_status = {}  # device index -> pinned int32 status word (created under _lock)
 launches = 0  # kernels-enqueuing library calls made by this process (bench bookkeeping)
 
 
@@ -76,6 +77,8 @@ def lib():
                 L.tritt_noalloc_scratch_bytes.restype = sz
                 L.tritt_selftest_umma.restype = i
                 L.tritt_selftest_umma.argtypes = [vp] * 5 + [i, vp, vp]
+                L.tritt_selftest_wait_expiry.restype = i
+                L.tritt_selftest_wait_expiry.argtypes = [i, C.c_longlong, vp, vp]
                 _lib = L
     return _lib
 
@@ -95,23 +98,63 @@ def _check(rc: int, what: str):
         raise TrittError(f"{what}: {msg} (CUDA error {rc})")
 
 
-def status_word(device: torch.device) -> torch.Tensor:
-    """Per-device int32 that kernels OR a code into when a bounded barrier wait ran out."""
-    key = torch.device(device).index
+STATUS_BITS = {1: "self-test kernel", 2: "triple-dot-product forward", 4: "triple-dot-product backward",
+               8: "shared memory of a tensor-core kernel was not 1024-byte aligned",
+               16: "soft-max attention forward (dot-product-sum)", 32: "soft-max attention backward (dot-product-sum)",
+               128: "wait-expiry self-test"}
+
+
+def _device_index(device) -> int:
+    d = torch.device(device)
+    return torch.cuda.current_device() if d.index is None else d.index
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 that kernels OR a code into when a bounded barrier wait ran out.
+
+    The word lives in page-locked host memory, which the GPU addresses directly (unified addressing): only a
+    kernel that gives up ever writes it, and the host can look at it without a copy or a synchronisation."""
+    key = _device_index(device)
     t = _status.get(key)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=device)
-        _status[key] = t
+        with _lock:
+            t = _status.get(key)
+            if t is None:
+                t = torch.zeros(1, dtype=torch.int32).pin_memory()
+                _status[key] = t
     return t
 
 
+def _describe(v: int) -> str:
+    return ", ".join(name for bit, name in STATUS_BITS.items() if v & bit) or f"code {v}"
+
+
 def read_status(device) -> int:
-    """Synchronises and returns (then clears) the device's kernel status word."""
+    """Synchronises the device and returns (then clears) its kernel status word."""
+    torch.cuda.synchronize(torch.device("cuda", _device_index(device)))
     t = status_word(device)
-    v = int(t.item())
+    v = int(t[0])
     if v:
         t.zero_()
     return v
+
+
+def check_status(device=None, synchronize: bool = True) -> None:
+    """Raises ``TrittError`` if a kernel enqueued earlier on ``device`` gave up on a bounded wait (its results are
+    then invalid).  With ``synchronize=False`` only kernels that have already finished are seen; every compute
+    entry point of this module makes that cheap check on entry, so a time-out surfaces at the latest on the next
+    call after the failed kernel has retired."""
+    dev = _device_index(torch.cuda.current_device() if device is None else device)
+    if synchronize:
+        v = read_status(dev)
+    else:
+        t = status_word(dev)
+        v = int(t[0])
+        if v:
+            t.zero_()
+    if v:
+        raise TrittError(f"a kernel of an earlier call on cuda:{dev} gave up waiting on a barrier after its time "
+                         f"limit ({_describe(v)}); the results of that call are invalid")
 
 
 def workspace(op: int, B: int, N: int, T: int, D: int, dtype: int, device) -> torch.Tensor:
@@ -148,6 +191,7 @@ def tdp_fwd(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr, q_mod=
     global launches
     B, N, T, D = q.shape
     dt = dtype_code(q.dtype)
+    check_status(q.device, synchronize=False)
     with torch.cuda.device(q.device):
         if ws is None:
             ws = workspace(OP_TDP_FWD, B, N, T, D, dt, q.device)
@@ -166,6 +210,7 @@ def tdp_bwd(q, k1, k2, v1, v2, o, do, lse, dq, dk1, dk2, dv1, dv2, alpha, causal
     B, N, T, D = q.shape
     dt = dtype_code(q.dtype)
     ptr = lambda t: 0 if t is None else t.data_ptr()
+    check_status(q.device, synchronize=False)
     with torch.cuda.device(q.device):
         if ws is None:
             ws = workspace(OP_TDP_BWD, B, N, T, D, dt, q.device)
@@ -182,6 +227,7 @@ def tdp_bwd(q, k1, k2, v1, v2, o, do, lse, dq, dk1, dk2, dv1, dv2, alpha, causal
 def tdp_bwd_finalize(v1, dk1, dk2, dv1, dv2, ws):
     global launches
     B, N, T, D = v1.shape
+    check_status(v1.device, synchronize=False)
     with torch.cuda.device(v1.device):
         rc = lib().tritt_tdp_bwd_finalize(v1.data_ptr(), dk1.data_ptr(), dk2.data_ptr(), dv1.data_ptr(),
                                           dv2.data_ptr(), B, N, T, D, dtype_code(v1.dtype), ws.data_ptr(),
@@ -194,6 +240,7 @@ def dps_fwd(q, k1, k2, v1, v2, o, m, alpha, causal, k_diff, flags=0):
     global launches
     B, N, T, D = q.shape
     dt = dtype_code(q.dtype)
+    check_status(q.device, synchronize=False)
     with torch.cuda.device(q.device):
         ws = workspace(OP_DPS_FWD, B, N, T, D, dt, q.device)
         rc = lib().tritt_dps_fwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
@@ -208,6 +255,7 @@ def dps_bwd(q, k1, k2, v1, v2, o, do, m, dq, dk1, dk2, dv1, dv2, alpha, causal, 
     global launches
     B, N, T, D = q.shape
     dt = dtype_code(q.dtype)
+    check_status(q.device, synchronize=False)
     with torch.cuda.device(q.device):
         ws = workspace(OP_DPS_BWD, B, N, T, D, dt, q.device)
         rc = lib().tritt_dps_bwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
@@ -225,6 +273,7 @@ def tdp_fwd_noalloc(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr
     Calls on one GPU must not overlap in time."""
     global launches
     B, N, T, D = q.shape
+    check_status(q.device, synchronize=False)
     with torch.cuda.device(q.device):
         rc = lib().tritt_tdp_fwd_noalloc(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
                                          o.data_ptr(), lse.data_ptr(), B, N, T, D, dtype_code(q.dtype), float(alpha),

@@ -36,7 +36,11 @@ class TrittentionTritonFunction(torch.autograd.Function):
         q, k1, k2, v1, v2 = (_native.aligned(t) for t in (q, k1, k2, v1, v2))
         o = torch.empty_like(q)
         m = torch.empty(q.shape[:3], device=q.device, dtype=torch.float32)
-        _native.dps_fwd(q, k1, k2, v1, v2, o, m, softmax_scale, causal, k_diff)
+        # convert_to_float32 asks for fp32 operands inside the kernels (reference trittention_triton.py:98-117
+        # forwards it to its launches): the CUDA-core path computes in fp32 on every dtype
+        flags = _native.FLAG_FORCE_SIMT if convert_to_float32 else 0
+        _native.dps_fwd(q, k1, k2, v1, v2, o, m, softmax_scale, causal, k_diff, flags=flags)
+        ctx.flags = flags
         ctx.causal = causal
         ctx.softmax_scale = softmax_scale
         ctx.k_diff = k_diff
@@ -53,7 +57,7 @@ class TrittentionTritonFunction(torch.autograd.Function):
         grad_output = _native.aligned(grad_output)
         dq, dk1, dk2, dv1, dv2 = (torch.empty_like(q) for _ in range(5))
         _native.dps_bwd(q, k1, k2, v1, v2, o, grad_output, m, dq, dk1, dk2, dv1, dv2, ctx.softmax_scale,
-                        ctx.causal, ctx.k_diff)
+                        ctx.causal, ctx.k_diff, flags=ctx.flags)
         return dq, dk1, dk2, dv1, dv2, None, None, None, None, None
 
 
@@ -78,8 +82,10 @@ class TrittentionTriton(nn.Module):
 
         ``S[q,s,t] = softmax_scale * (q[q].k2[t] + k1[s].k2[t])``, causal mask
         ``s <= t <= q`` and ``t - s <= k_diff``; ``o = sum_st P SiLU(v1[s]) v2[t]``.
-        All arithmetic is fp32 on every dtype, so ``convert_to_float32`` and
-        ``input_precision`` need no special handling.
+        16-bit inputs with a head dimension of 64 or 128 run on the tensor cores with 16-bit operands (the
+        probabilities and ``Y*V2`` are rounded to the inputs' type, accumulation and soft-max state are fp32);
+        ``convert_to_float32=True`` selects the fp32 CUDA-core kernels instead, as do fp32 inputs and other
+        head dimensions.  ``input_precision`` is accepted for interface parity and has no effect.
         """
         return TrittentionTritonFunction.apply(q, k1, k2, v1, v2, self.causal, self.softmax_scale, self.k_diff,
                                                self.convert_to_float32, self.input_precision)

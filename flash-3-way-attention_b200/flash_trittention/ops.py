@@ -116,19 +116,21 @@ def tdp_attention(q, k1, k2, v1, v2, softmax_scale=1 / 8, causal=True, k1_window
 
 @torch.library.custom_op("flash_trittention::dps_fwd", mutates_args=(), device_types="cuda")
 def dps_fwd(q: Tensor, k1: Tensor, k2: Tensor, v1: Tensor, v2: Tensor, softmax_scale: float, causal: bool,
-            k_diff: int) -> Tuple[Tensor, Tensor]:
-    """``(o [B,N,S,D], m [B,N,S] fp32 log-sum-exp)`` of ``tritt_dps_fwd``."""
+            k_diff: int, convert_to_float32: bool = False) -> Tuple[Tensor, Tensor]:
+    """``(o [B,N,S,D], m [B,N,S] fp32 log-sum-exp)`` of ``tritt_dps_fwd``; ``convert_to_float32`` selects the
+    fp32 CUDA-core kernels on every dtype."""
     _check_inputs(q, k1, k2, v1, v2)
     _native.dtype_code(q.dtype)
     q, k1, k2, v1, v2 = (_native.aligned(t) for t in (q, k1, k2, v1, v2))
     o = torch.empty_like(q)
     m = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
-    _native.dps_fwd(q, k1, k2, v1, v2, o, m, softmax_scale, causal, k_diff)
+    _native.dps_fwd(q, k1, k2, v1, v2, o, m, softmax_scale, causal, k_diff,
+                    flags=_native.FLAG_FORCE_SIMT if convert_to_float32 else 0)
     return o, m
 
 
 @dps_fwd.register_fake
-def _(q, k1, k2, v1, v2, softmax_scale, causal, k_diff):
+def _(q, k1, k2, v1, v2, softmax_scale, causal, k_diff, convert_to_float32=False):
     _check_inputs(q, k1, k2, v1, v2)
     return (torch.empty(q.shape, dtype=q.dtype, device=q.device),
             torch.empty(q.shape[:3], dtype=torch.float32, device=q.device))
@@ -136,16 +138,18 @@ def _(q, k1, k2, v1, v2, softmax_scale, causal, k_diff):
 
 @torch.library.custom_op("flash_trittention::dps_bwd", mutates_args=(), device_types="cuda")
 def dps_bwd(q: Tensor, k1: Tensor, k2: Tensor, v1: Tensor, v2: Tensor, o: Tensor, d_o: Tensor, m: Tensor,
-            softmax_scale: float, causal: bool, k_diff: int) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+            softmax_scale: float, causal: bool, k_diff: int,
+            convert_to_float32: bool = False) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
     q, k1, k2, v1, v2, o, m = (_native.aligned(t) for t in (q, k1, k2, v1, v2, o, m))
     d_o = _native.aligned(d_o.to(q.dtype))
     grads = tuple(torch.empty_like(q) for _ in range(5))
-    _native.dps_bwd(q, k1, k2, v1, v2, o, d_o, m, *grads, softmax_scale, causal, k_diff)
+    _native.dps_bwd(q, k1, k2, v1, v2, o, d_o, m, *grads, softmax_scale, causal, k_diff,
+                    flags=_native.FLAG_FORCE_SIMT if convert_to_float32 else 0)
     return grads
 
 
 @dps_bwd.register_fake
-def _(q, k1, k2, v1, v2, o, d_o, m, softmax_scale, causal, k_diff):
+def _(q, k1, k2, v1, v2, o, d_o, m, softmax_scale, causal, k_diff, convert_to_float32=False):
     return tuple(torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(5))
 
 
@@ -159,15 +163,15 @@ def _dps_setup(ctx, inputs, output):
 
 def _dps_backward(ctx, d_o, d_m):
     grads = dps_bwd(*ctx.saved_tensors[:6], d_o, ctx.saved_tensors[6], *ctx.rest)
-    return (*grads, None, None, None)
+    return (*grads, None, None, None, None)
 
 
 dps_fwd.register_autograd(_dps_backward, setup_context=_dps_setup)
 
 
-def dps_attention(q, k1, k2, v1, v2, softmax_scale=1 / 8, causal=True, k_diff=1024):
+def dps_attention(q, k1, k2, v1, v2, softmax_scale=1 / 8, causal=True, k_diff=1024, convert_to_float32=False):
     """Differentiable dot-product-sum trittention through the registered operators: ``(o, m)``."""
-    return dps_fwd(q, k1, k2, v1, v2, float(softmax_scale), bool(causal), int(k_diff))
+    return dps_fwd(q, k1, k2, v1, v2, float(softmax_scale), bool(causal), int(k_diff), bool(convert_to_float32))
 
 
 # ------------------------------------------------------------------ module

@@ -16,9 +16,15 @@
  *   - calls only enqueue work on `stream` (no synchronisation, no device allocation);
  *   - return value 0 = success, negative = invalid argument, positive = cudaError_t of
  *     a failed runtime call.  tritt_last_error() gives a thread-local message;
- *   - `status_word` (device int, may be NULL) is OR-ed with a non-zero code by a kernel
- *     whose bounded barrier wait ran out; the caller zeroes and reads it;
- *   - window arguments follow the reference: a value >= T (or < 0) means "unlimited".
+ *   - `status_word` (an int the GPU can address: device memory or page-locked host memory; may be NULL)
+ *     is OR-ed with a non-zero code by a kernel whose bounded barrier wait ran out (1 tensor-core
+ *     self-test, 2 / 4 triple-dot-product forward / backward, 8 misaligned shared memory, 16 / 32
+ *     soft-max attention forward / backward of the dot-product-sum path, 128 wait-expiry self-test);
+ *     the caller zeroes and reads it.  A non-zero word means the results of that call are invalid;
+ *   - window arguments (k1_window, k2_window, kk_left, kk_right, k_diff) are distances >= 0; a value
+ *     >= T means "unlimited".  Negative values are refused with an argument error when `causal` is set
+ *     (the reference applies them literally, which leaves query rows with nothing to attend to);
+ *   - B*N may not exceed 65535.
  */
 #ifndef TRITT_H_
 #define TRITT_H_
@@ -62,8 +68,8 @@ size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype);
 /* Which kernel family a TDP call with these arguments runs on. */
 int tritt_tdp_path(int op, int T, int D, int dtype, int causal, int k1_window, int k2_window, int kk_left,
                    int kk_right, int flags);
-/* Which kernel family the two soft-max attentions of a DPS forward run on (the backward recomputes its inner leg on
-   the same family and differentiates on the CUDA cores). */
+/* Which kernel family the two soft-max attentions of a DPS forward, and their row-owner / column-owner backward
+   kernels, run on. */
 int tritt_dps_path(int T, int D, int dtype, int k_diff, int flags);
 
 /*
@@ -129,12 +135,15 @@ int tritt_dps_bwd(const void* q, const void* k1, const void* k2, const void* v1,
  * another program's enqueue hook, a process whose device memory all belongs to a pool this call
  * site cannot use, a section that must avoid the allocator's device-wide synchronisation).
  * Same computation and checks as tritt_tdp_fwd for all query rows, but the scratch is an 8 MiB array
- * built into the library image (tritt_noalloc_scratch_bytes()), held by every GPU that loads the
- * library until the process exits.  Limits: 16-bit inputs with B*N*T*D > 4 194 304 elements are
- * rejected (fp32 inputs need no scratch); calls that overlap in time on one GPU share the array and
- * race; the first call on a device resolves the array's address and should precede any stream
- * capture on that device.  It calls no allocation routine.  This entry point has no counterpart in
- * the reference.
+ * built into the library image (tritt_noalloc_scratch_bytes()), held by every GPU whose context has
+ * loaded that image until the process exits (with CUDA's lazy module loading the driver may load it,
+ * and reserve its memory, only at the first call).  Limits: 16-bit inputs on the tensor-core path
+ * (head dimension 64 or 128) with B*N*T*D > 4 194 304 elements are rejected (the CUDA-core path - fp32
+ * inputs, other head dimensions, TRITT_FLAG_FORCE_SIMT - needs no scratch); calls that overlap in time
+ * on one GPU share the array and race; the first call on a device resolves the array's address and
+ * should precede any stream capture on that device; the cached address does not survive
+ * cudaDeviceReset.  It calls no allocation routine of the CUDA runtime or of any library.  This entry
+ * point has no counterpart in the reference.
  */
 int tritt_tdp_fwd_noalloc(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, void* o,
                           float* lse, int B, int N, int T, int D, int dtype, float alpha, int causal,
@@ -151,6 +160,15 @@ size_t tritt_noalloc_scratch_bytes(void);
  */
 int tritt_selftest_umma(const void* A, const void* Bm, const void* V, float* C, float* C2, int dtype,
                         int* status_word, tritt_stream_t stream);
+
+/*
+ * Self-test of the bounded barrier wait that every tensor-core kernel uses: a one-CTA kernel in which one
+ * thread is to arrive on an mbarrier and a warp waits for it, giving up after `limit_ticks` clock ticks
+ * (1 .. 2e9).  With skip_arrival != 0 the arrival is left out on purpose: the wait runs out, the kernel ORs
+ * 128 into `status_word`, frees its tensor memory and returns; nothing faults and the context stays usable.
+ * No counterpart in the reference (Triton kernels have no hand-written waits).
+ */
+int tritt_selftest_wait_expiry(int skip_arrival, long long limit_ticks, int* status_word, tritt_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -67,8 +67,8 @@ def tdp_valid_mask(q_idx: torch.Tensor, T: int, causal: bool, windows) -> Option
         return None
     k1w, k2w, kkl, kkr = windows
     q = q_idx.view(-1, 1, 1)
-    j = torch.arange(T).view(1, -1, 1)
-    k = torch.arange(T).view(1, 1, -1)
+    j = torch.arange(T, device=q_idx.device).view(1, -1, 1)
+    k = torch.arange(T, device=q_idx.device).view(1, 1, -1)
     return (
         (j <= q) & (q <= j + k1w) & (k <= q) & (q <= k + k2w) & (j + kkl >= k) & (k + kkr >= j)
     )
@@ -116,21 +116,25 @@ def _tdp_scores(qc, k1, k2, alpha):
 def tdp_forward(
     q, k1, k2, v1, v2, softmax_scale: float, causal: bool = True,
     k1_window=None, k2_window=None, kk_left=None, kk_right=None,
-    chunk: Optional[int] = None, dtype=torch.float32,
+    chunk: Optional[int] = None, dtype=torch.float32, device="cpu",
 ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Returns ``(z [B,N,T,D], lse [B,N,T])`` (natural-log log-sum-exp of the scaled logits)."""
+    """Returns ``(z [B,N,T,D], lse [B,N,T])`` (natural-log log-sum-exp of the scaled logits).
+
+    ``device``: where the restatement is evaluated.  The default is the CPU; the benchmark-size parity tests
+    pass a CUDA device (with TF32 matmuls switched off) because one head at T = 2048 takes minutes on host cores.
+    """
     B, N, T, D = q.shape
     windows = resolve_windows(T, k1_window, k2_window, kk_left, kk_right)
-    q, k1, k2, v1, v2 = (t.detach().to("cpu", dtype) for t in (q, k1, k2, v1, v2))
-    z = torch.empty(B, N, T, D, dtype=dtype)
-    lse = torch.empty(B, N, T, dtype=dtype)
+    q, k1, k2, v1, v2 = (t.detach().to(device, dtype) for t in (q, k1, k2, v1, v2))
+    z = torch.empty(B, N, T, D, dtype=dtype, device=device)
+    lse = torch.empty(B, N, T, dtype=dtype, device=device)
     ch = _auto_chunk(T, chunk)
     for b in range(B):
         for n in range(N):
             sv1 = F.silu(v1[b, n])
             for q0, q1 in _chunks(T, ch):
                 s = _tdp_scores(q[b, n, q0:q1], k1[b, n], k2[b, n], softmax_scale)
-                m = tdp_valid_mask(torch.arange(q0, q1), T, causal, windows)
+                m = tdp_valid_mask(torch.arange(q0, q1, device=device), T, causal, windows)
                 if m is not None:
                     s = s.masked_fill(~m, float("-inf"))
                 l = torch.logsumexp(s.reshape(q1 - q0, -1), dim=-1)
@@ -145,9 +149,9 @@ def tdp_forward(
 def tdp_backward(
     q, k1, k2, v1, v2, dz, softmax_scale: float, causal: bool = True,
     k1_window=None, k2_window=None, kk_left=None, kk_right=None,
-    chunk: Optional[int] = None, dtype=torch.float32,
+    chunk: Optional[int] = None, dtype=torch.float32, device="cpu",
 ):
-    """Explicit backward; returns ``(dq, dk1, dk2, dv1, dv2)``.
+    """Explicit backward; returns ``(dq, dk1, dk2, dv1, dv2)`` (on ``device``, see ``tdp_forward``).
 
     With ``sV1 = SiLU(V1)``, ``Dq = sum_h dZ*Z``, ``dP = sum_h dZ[q] sV1[j] V2[k]`` and
     ``dS = P * (dP - Dq)``: ``dQ = a*sum_jk dS K1 K2``, ``dK1 = a*sum_qk dS Q K2``,
@@ -156,7 +160,7 @@ def tdp_backward(
     """
     B, N, T, D = q.shape
     windows = resolve_windows(T, k1_window, k2_window, kk_left, kk_right)
-    q, k1, k2, v1, v2, dz = (t.detach().to("cpu", dtype) for t in (q, k1, k2, v1, v2, dz))
+    q, k1, k2, v1, v2, dz = (t.detach().to(device, dtype) for t in (q, k1, k2, v1, v2, dz))
     dq = torch.zeros_like(q)
     dk1 = torch.zeros_like(q)
     dk2 = torch.zeros_like(q)
@@ -171,7 +175,7 @@ def tdp_backward(
             for q0, q1 in _chunks(T, ch):
                 Qc, dZc = q[b, n, q0:q1], dz[b, n, q0:q1]
                 s = _tdp_scores(Qc, K1, K2, a)
-                m = tdp_valid_mask(torch.arange(q0, q1), T, causal, windows)
+                m = tdp_valid_mask(torch.arange(q0, q1, device=device), T, causal, windows)
                 if m is not None:
                     s = s.masked_fill(~m, float("-inf"))
                 l = torch.logsumexp(s.reshape(q1 - q0, -1), dim=-1)

@@ -1,44 +1,25 @@
 """Parity at the sequence lengths and head dimensions of the benchmark configurations, where the dense oracle
-cannot run.  Triple-dot-product (T=2048, D=128 and T=4096, D=64, bf16, causal, alpha = 1/D): sampled query rows
-against an fp32 per-row evaluation of the same formulas, and size-independent properties of the backward (linearity
-in the upstream gradient, query-row shards summing to the full gradient).  Dot-product-sum (T=1024, D=64, fp16):
+cannot run on the host.  Triple-dot-product (T=2048, D=128 and T=4096, D=64, bf16, causal, alpha = 1/D): whole
+heads (output, log-sum-exp, all five gradients) against the oracle evaluated in fp32 on the GPU, and
+size-independent properties of the backward (linearity in the upstream gradient, query-row shards summing to the
+full gradient).  Dot-product-sum (T=1024, D=64, fp16):
 the whole result against the factorised fp32 formulation on the CPU."""
 import pytest
 import torch
 
+from _parity import assert_close, fmt
 from oracle import trittention_oracle as orc
 from flash_trittention import _native
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-TOL = 2e-2  # max-abs error of bf16 results against fp32, relative to max(1, magnitude)
 
 
-def _row_reference(q, k1, k2, v1, v2, do, o, alpha, rows):
-    """fp32 evaluation of a few query rows of one head (tensors [T, D] on the GPU, TF32 off): returns
-    O[rows], lse[rows], dQ[rows].  Formulas: S = alpha (Q[q] * K1) K2^T over j, k <= q; P = softmax;
-    O = sum_jk P SiLU(V1[j]) V2[k]; dP = (dO * SiLU(V1)) V2^T; dS = P (dP - sum_h dO O); dQ = alpha sum_jk dS K1[j] K2[k]."""
-    sv1 = torch.nn.functional.silu(v1)
-    outs, lses, dqs = [], [], []
-    for r in rows:
-        n = r + 1
-        s = alpha * ((q[r] * k1[:n]) @ k2[:n].T)          # [j, k]
-        m = s.max()
-        e = torch.exp(s - m)
-        l = e.sum()
-        p = e / l
-        o_r = ((p @ v2[:n]) * sv1[:n]).sum(0)             # sum_j SiLU(V1[j]) * sum_k P[j,k] V2[k]
-        dp = (do[r] * sv1[:n]) @ v2[:n].T
-        ds = p * (dp - (do[r] * o_r).sum())
-        dq = alpha * ((ds @ k2[:n]) * k1[:n]).sum(0)
-        outs.append(o_r)
-        lses.append(m + torch.log(l))
-        dqs.append(dq)
-    return torch.stack(outs), torch.stack(lses), torch.stack(dqs)
-
-
-@pytest.mark.parametrize("T,D", [(2048, 128), (4096, 64)])
-def test_sampled_rows_at_benchmark_sizes(T, D):
+@pytest.mark.parametrize("T,D,heads_checked", [(2048, 128, 2), (4096, 64, 1)])
+def test_whole_heads_at_benchmark_sizes(T, D, heads_checked):
+    """Output, log-sum-exp and all five gradients of whole heads at the benchmark shapes (bf16, causal, full
+    windows, inputs N(0,1)*0.5, alpha = 1/D) against the oracle evaluated in fp32 on the GPU (TF32 off).  Every
+    tensor is bounded against its own magnitude; the normalised errors are printed (run pytest with -s)."""
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     try:
@@ -52,14 +33,21 @@ def test_sampled_rows_at_benchmark_sizes(T, D):
         _native.tdp_bwd(*t, o, do, lse, *g, alpha, True, None, None, None, None)
         torch.cuda.synchronize()
         assert _native.read_status(torch.device(DEV)) == 0
-        rows = [0, 1, 63, 64, 127, 128, 129, 255, 256, T // 2 - 1, T // 2, T - 129, T - 128, T - 2, T - 1]
-        for h in range(N):
-            f = [x[0, h].float() for x in t]
-            o_ref, lse_ref, dq_ref = _row_reference(*f, do[0, h].float(), o[0, h].float(), alpha, rows)
-            assert float((o[0, h, rows].float() - o_ref).abs().max()) <= TOL
-            assert float((lse[0, h, rows] - lse_ref).abs().max()) <= TOL
-            mag = max(1.0, float(dq_ref.abs().max()))
-            assert float((g[0][0, h, rows].float() - dq_ref).abs().max()) <= TOL * mag
+        chunk = max(1, (1 << 27) // (T * T))  # 512 MiB per [chunk, T, T] fp32 intermediate
+        for h in range(heads_checked):
+            f = [x[:, h:h + 1].float() for x in t]
+            z_ref, lse_ref = orc.tdp_forward(*f, alpha, True, chunk=chunk, device=DEV)
+            g_ref = orc.tdp_backward(*f, do[:, h:h + 1].float(), alpha, True, chunk=chunk, device=DEV)
+            rep = {}
+            try:
+                assert_close("o", o[:, h:h + 1], z_ref, torch.bfloat16, report=rep)
+                # late rows are averages over ~T^2 terms and therefore tiny: check them on their own as well
+                assert_close("o[T/2:]", o[:, h:h + 1, T // 2:], z_ref[:, :, T // 2:], torch.bfloat16, report=rep)
+                assert float((lse[:, h:h + 1] - lse_ref).abs().max()) <= 5e-3
+                for name, got, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), g, g_ref):
+                    assert_close(name, got[:, h:h + 1], ref, torch.bfloat16, report=rep)
+            finally:
+                print(f"\nT={T} D={D} bf16 head {h}: {fmt(rep)}")
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
 
@@ -84,9 +72,8 @@ def test_backward_is_linear_in_the_upstream_gradient_at_benchmark_size():
     torch.cuda.synchronize()
     assert _native.read_status(torch.device(DEV)) == 0
     for name, a, b, c in zip(("dq", "dk1", "dk2", "dv1", "dv2"), ga, gb, gc):
-        ref = 2 * a - b
-        mag = max(1.0, float(ref.abs().max()))
-        assert float((c - ref).abs().max()) <= 3 * TOL * mag, name
+        # three bf16-rounded results and a bf16-rounded input combination enter: twice the single-result bound
+        assert_close(name, c, 2 * a - b, torch.bfloat16, scale=2.0)
 
 
 def test_query_shards_sum_to_the_full_gradient_at_benchmark_size():
@@ -99,7 +86,7 @@ def test_query_shards_sum_to_the_full_gradient_at_benchmark_size():
     o2, lse2 = torch.zeros_like(o), torch.zeros_like(lse)
     for rem in range(8):
         _native.tdp_fwd(*t, o2, lse2, alpha, True, None, None, None, None, q_mod=8, q_rem=rem)
-    assert float((o2.float() - o.float()).abs().max()) <= 1e-2
+    assert_close("o (shards vs whole)", o2, o, torch.bfloat16)
     assert float((lse2 - lse).abs().max()) <= 1e-3
     full = [torch.empty_like(t[0]) for _ in range(5)]
     _native.tdp_bwd(*t, o, do, lse, *full, alpha, True, None, None, None, None)
@@ -117,8 +104,7 @@ def test_query_shards_sum_to_the_full_gradient_at_benchmark_size():
     torch.cuda.synchronize()
     assert _native.read_status(torch.device(DEV)) == 0
     for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), [dq] + outs, full):
-        mag = max(1.0, float(b.float().abs().max()))
-        assert float((a.float() - b.float()).abs().max()) <= TOL * mag, name
+        assert_close(name + " (shards vs whole)", a, b, torch.bfloat16)
 
 
 def _dps_factorised(q, k1, k2, v1, v2, a, k_diff):
@@ -153,8 +139,7 @@ def test_dot_product_sum_at_benchmark_size():
     ref_leaves = [x.float().requires_grad_(True) for x in (q, k1, k2, v1, v2)]
     z_ref, lse_ref = _dps_factorised(*ref_leaves, a, T)
     z_ref.backward(dz.float())
-    assert float((out.detach().float().cpu() - z_ref.detach()).abs().max()) <= 5e-3
+    assert_close("o", out.detach().cpu(), z_ref.detach(), torch.float16)
     assert float((m.cpu() - lse_ref.detach()).abs().max()) <= 5e-3
     for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, ref_leaves):
-        g, r = leaf.grad.float().cpu(), ref.grad
-        assert float((g - r).abs().max()) <= 5e-3 * max(1.0, float(r.abs().max())), name
+        assert_close(name, leaf.grad.cpu(), ref.grad, torch.float16)

@@ -17,7 +17,7 @@ def _same_grads(a, b):
     """Two runs of a backward agree up to the summation order of its fp32 atomic accumulation."""
     for x, y in zip(a, b):
         gx, gy = x.grad.float(), y.grad.float()
-        assert float((gx - gy).abs().max()) <= 4e-3 * max(1.0, float(gx.abs().max()))
+        assert float((gx - gy).abs().max()) <= 8e-3 * float(gx.abs().max())  # one bf16 ulp of the largest element
 
 
 def _meta(shape=(2, 3, 64, 32), dtype=torch.bfloat16, grad=True):

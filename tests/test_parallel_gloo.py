@@ -3,8 +3,9 @@
 The kernels cannot run here, so the two native calls the sharded path makes are replaced IN THIS
 TEST by stand-ins built on the CPU oracle that honour the same contract (interleaved query rows,
 fp32 partial key-side sums in the workspace).  What is under test is the distributed plumbing of
-``flash_trittention/parallel.py``: row ownership, the gather-by-sum of outputs, the all-reduce of
-the partial sums and the finalisation, and head sharding."""
+``flash_trittention/parallel.py``: row ownership, the all-gather of output and dQ rows (with a sequence
+length that does not divide by the world size), the forward that exchanges nothing when the caller does not ask for
+the gathered output, the all-reduce of the partial sums and the finalisation, and head sharding."""
 import os
 import sys
 
@@ -26,7 +27,7 @@ def _worker(rank, world, port, results):
         from flash_trittention import _native, parallel
         from oracle import trittention_oracle as orc
 
-        B, N, T, D, alpha = 1, 2, 24, 8, 0.25
+        B, N, T, D, alpha = 1, 2, 25, 8, 0.25
         q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, seed=3)
 
         def fake_fwd(q, k1, k2, v1, v2, o, lse, alpha, causal, *w, q_mod=1, q_rem=0, flags=0):
@@ -63,6 +64,20 @@ def _worker(rank, world, port, results):
             dv2.copy_(part[3 * n:4 * n].view_as(v1))
 
         _native.tdp_fwd, _native.tdp_bwd, _native.tdp_bwd_finalize = fake_fwd, fake_bwd, fake_finalize
+        # the product refuses CPU tensors; the stand-ins above do not need a device
+        from flash_trittention.triple_dot_product import flash_trittention as ft_mod
+
+        ft_mod._validate = lambda *a: None
+        _native.check_status = lambda *a, **k: None
+        collectives = []
+        for name in ("all_reduce", "all_gather_into_tensor"):
+            orig = getattr(dist, name)
+
+            def counted(*a, _orig=orig, _name=name, **k):
+                collectives.append(_name)
+                return _orig(*a, **k)
+
+            setattr(dist, name, counted)
         leaves = [t.clone().requires_grad_(True) for t in (q, k1, k2, v1, v2)]
         out = parallel.flash_trittention_query_sharded(*leaves, alpha, True)
         out.backward(dz)
@@ -71,6 +86,16 @@ def _worker(rank, world, port, results):
         ok = torch.allclose(out, z_ref, atol=1e-5)
         for leaf, ref in zip(leaves, g_ref):
             ok = ok and torch.allclose(leaf.grad, ref, atol=2e-4)
+        # one gather forward; backward = one all-reduce (the partial sums) + one gather (dQ rows)
+        ok = ok and collectives == ["all_gather_into_tensor", "all_reduce", "all_gather_into_tensor"]
+        # without the gathered output the forward does not communicate, and only the own rows are filled in
+        del collectives[:]
+        with torch.no_grad():
+            own = parallel.flash_trittention_query_sharded(q, k1, k2, v1, v2, alpha, True, None, False)
+        rows = parallel.owned_rows(T, rank, world)
+        other = parallel.owned_rows(T, 1 - rank, world)
+        ok = ok and collectives == [] and torch.allclose(own[:, :, rows], z_ref[:, :, rows], atol=1e-5)
+        ok = ok and bool((own[:, :, other] == 0).all())
         # head sharding: the ranks' slices tile the (batch*head) axis exactly once
         full = torch.arange(2 * 3 * 4 * 5, dtype=torch.float32).view(2, 3, 4, 5)
         mine = parallel.shard_heads(full, rank, world)

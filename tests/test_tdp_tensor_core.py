@@ -1,8 +1,11 @@
 """Parity of the tensor-core (tcgen05) triple-dot-product path with the fp32 CPU oracle on
-the same 16-bit-rounded inputs: max-abs error <= 2e-2 (bf16) / 5e-3 (fp16)."""
+the same 16-bit-rounded inputs.  Every result tensor (output and each of the five gradients) is bounded
+against its own magnitude: max|err| <= 2e-2 max|ref| (bf16) / 5e-3 max|ref| (fp16), and the same two
+figures for the relative rms error, so that an all-zero or mis-scaled tensor fails whatever its size."""
 import pytest
 import torch
 
+from _parity import assert_close, fmt
 from oracle import trittention_oracle as orc
 from flash_trittention import _native
 from flash_trittention.triple_dot_product.flash_trittention import flash_trittention
@@ -12,7 +15,7 @@ DEV = "cuda:0"
 TOL = {torch.bfloat16: 2e-2, torch.float16: 5e-3}
 
 
-def _fwd_case(B, N, T, D, dtype, causal, scale_in, alpha, seed):
+def _fwd_case(B, N, T, D, dtype, causal, scale_in, alpha, seed, o_scale=1.0):
     q, k1, k2, v1, v2, _ = orc.make_inputs(B, N, T, D, scale=scale_in, seed=seed, dtype=dtype)
     code = _native.dtype_code(dtype)
     assert _native.tdp_path(_native.OP_TDP_FWD, T, D, code, causal, None, None, None, None) == _native.PATH_TCGEN05
@@ -23,9 +26,11 @@ def _fwd_case(B, N, T, D, dtype, causal, scale_in, alpha, seed):
     torch.cuda.synchronize()
     assert _native.read_status(torch.device(DEV)) == 0, "a bounded barrier wait ran out"
     z_ref, lse_ref = orc.tdp_forward(*(t.float() for t in (q, k1, k2, v1, v2)), alpha, causal)
-    err = float((o.float().cpu() - z_ref).abs().max())
+    rep = {}
+    assert_close("o", o.cpu(), z_ref, dtype, scale=o_scale, report=rep)
+    print(f"\nfwd T={T} D={D} {dtype} causal={causal}: {fmt(rep)}")
     lerr = float((lse.cpu() - lse_ref).abs().max())
-    return err, lerr
+    return lerr
 
 
 @pytest.mark.parametrize("D", [64, 128])
@@ -34,25 +39,25 @@ def _fwd_case(B, N, T, D, dtype, causal, scale_in, alpha, seed):
 def test_forward_bf16_matches_oracle(T, D, causal):
     if not causal and T > 256:
         pytest.skip("dense oracle too slow")
-    err, lerr = _fwd_case(1, 2, T, D, torch.bfloat16, causal, 0.5, 1.0 / D, seed=T + D)
-    assert err <= TOL[torch.bfloat16], err
-    assert lerr <= 2e-2, lerr
+    lerr = _fwd_case(1, 2, T, D, torch.bfloat16, causal, 0.5, 1.0 / D, seed=T + D)
+    assert lerr <= 5e-3, lerr
 
 
 @pytest.mark.parametrize("D", [64, 128])
 def test_forward_fp16_matches_oracle(D):
-    err, lerr = _fwd_case(2, 2, 200, D, torch.float16, True, 0.5, 1.0 / D, seed=3)
-    assert err <= TOL[torch.float16], err
-    assert lerr <= 5e-3, lerr
+    lerr = _fwd_case(2, 2, 200, D, torch.float16, True, 0.5, 1.0 / D, seed=3)
+    assert lerr <= 1e-3, lerr
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_forward_unit_variance_inputs_large_logits(dtype):
-    """N(0,1) inputs with alpha = 1/8 (the reference tests' setting) give logits of order 1-10 and make
-    the running maximum move, which exercises the accumulator rescaling."""
-    err, lerr = _fwd_case(1, 2, 192, 64, dtype, True, 1.0, 1 / 8, seed=17)
-    # bf16 pre-products perturb O(1) logits by ~1e-2, so the bound is looser than for the benchmark inputs
-    assert err <= (6e-2 if dtype == torch.bfloat16 else 1e-2), err
+def test_forward_reference_test_distribution(dtype, D, causal):
+    """The reference tests' own setting (tests/test_triple_dot_product.py:51-96 there): N(0,1) inputs with
+    alpha = 1/8.  Logits are of order 1-10, so the running maximum moves (accumulator rescaling) and the
+    16-bit rounding of the pre-product Q*K2 shows in the scores."""
+    lerr = _fwd_case(1, 2, 192 if causal else 96, D, dtype, causal, 1.0, 1 / 8, seed=17 + D)
+    assert lerr <= (2e-2 if dtype == torch.bfloat16 else 5e-3), lerr
 
 
 def test_forward_matches_cuda_core_path_and_query_shards():
@@ -66,8 +71,8 @@ def test_forward_matches_cuda_core_path_and_query_shards():
         _native.tdp_fwd(*t, o, lse, 1 / D, True, None, None, None, None, q_mod=4, q_rem=rem)
     torch.cuda.synchronize()
     assert _native.read_status(torch.device(DEV)) == 0
-    assert float((o.float() - o_ref.float()).abs().max()) <= 2e-2
-    assert float((lse - lse_ref).abs().max()) <= 2e-2
+    assert_close("o vs cuda-core path", o, o_ref, torch.bfloat16)
+    assert float((lse - lse_ref).abs().max()) <= 5e-3
 
 
 def test_autograd_entry_point_uses_tensor_core_forward():
@@ -80,9 +85,9 @@ def test_autograd_entry_point_uses_tensor_core_forward():
     f = [x.float() for x in (q, k1, k2, v1, v2)]
     z_ref, _ = orc.tdp_forward(*f, 1 / D, True)
     g_ref = orc.tdp_backward(*f, dz.float(), 1 / D, True)
-    assert float((out.float().cpu() - z_ref).abs().max()) <= 2e-2
+    assert_close("o", out.cpu(), z_ref, torch.bfloat16)
     for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, g_ref):
-        assert float((leaf.grad.float().cpu() - ref).abs().max()) <= 2e-2 * max(1.0, float(ref.abs().max())), name
+        assert_close(name, leaf.grad.cpu(), ref, torch.bfloat16)
 
 
 def _bwd_case(B, N, T, D, dtype, causal, scale_in, alpha, seed):
@@ -96,32 +101,33 @@ def _bwd_case(B, N, T, D, dtype, causal, scale_in, alpha, seed):
     assert _native.read_status(torch.device(DEV)) == 0, "a bounded barrier wait ran out"
     f = [x.float() for x in (q, k1, k2, v1, v2)]
     g_ref = orc.tdp_backward(*f, dz.float(), alpha, causal)
-    errs = {}
-    for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, g_ref):
-        errs[name] = (float((leaf.grad.float().cpu() - ref).abs().max()), float(ref.abs().max()))
-    return errs
+    rep = {}
+    try:
+        for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, g_ref):
+            assert_close(name, leaf.grad.cpu(), ref, dtype, report=rep)
+    finally:
+        print(f"\nbwd T={T} D={D} {dtype} causal={causal}: {fmt(rep)}")
 
 
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("T", [40, 64, 100, 129, 256])
 @pytest.mark.parametrize("causal", [True, False])
 def test_backward_bf16_matches_oracle(T, D, causal):
-    errs = _bwd_case(1, 2, T, D, torch.bfloat16, causal, 0.5, 1.0 / D, seed=2 * T + D)
-    for name, (err, mag) in errs.items():
-        assert err <= TOL[torch.bfloat16] * max(1.0, mag), (name, err, mag)
+    _bwd_case(1, 2, T, D, torch.bfloat16, causal, 0.5, 1.0 / D, seed=2 * T + D)
 
 
 @pytest.mark.parametrize("D", [64, 128])
 def test_backward_fp16_matches_oracle(D):
-    errs = _bwd_case(2, 2, 200, D, torch.float16, True, 0.5, 1.0 / D, seed=4)
-    for name, (err, mag) in errs.items():
-        assert err <= TOL[torch.float16] * max(1.0, mag), (name, err, mag)
+    _bwd_case(2, 2, 200, D, torch.float16, True, 0.5, 1.0 / D, seed=4)
 
 
-def test_backward_unit_variance_inputs():
-    errs = _bwd_case(1, 2, 160, 64, torch.float16, True, 1.0, 1 / 8, seed=19)
-    for name, (err, mag) in errs.items():
-        assert err <= 2e-2 * max(1.0, mag), (name, err, mag)
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_backward_reference_test_distribution(dtype, D, causal):
+    """All five gradients on the reference tests' distribution (N(0,1), alpha = 1/8), both 16-bit types, both
+    head dimensions, causal and not."""
+    _bwd_case(1, 2, 160 if causal else 96, D, dtype, causal, 1.0, 1 / 8, seed=19 + D)
 
 
 def test_backward_query_shards_sum_to_full_gradient():
@@ -150,7 +156,7 @@ def test_backward_query_shards_sum_to_full_gradient():
     torch.cuda.synchronize()
     assert _native.read_status(torch.device(DEV)) == 0
     for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), [dq] + outs, full):
-        assert float((a.float() - b.float()).abs().max()) <= 2e-2 * max(1.0, float(b.float().abs().max())), name
+        assert_close(name + " (shards vs whole)", a, b, torch.bfloat16)
 
 
 WINDOWS = [
@@ -181,9 +187,9 @@ def test_forward_windows_match_oracle(windows, D):
     torch.cuda.synchronize()
     assert _native.read_status(torch.device(DEV)) == 0, "a bounded barrier wait ran out"
     z_ref, lse_ref = orc.tdp_forward(*(t.float() for t in (q, k1, k2, v1, v2)), 1.0 / D, True, *windows)
-    assert torch.isfinite(o.float()).all() and torch.isfinite(lse).all()
-    assert float((o.float().cpu() - z_ref).abs().max()) <= TOL[dtype]
-    assert float((lse.cpu() - lse_ref).abs().max()) <= 2e-2
+    assert torch.isfinite(lse).all()
+    assert_close("o", o.cpu(), z_ref, dtype)
+    assert float((lse.cpu() - lse_ref).abs().max()) <= 5e-3
 
 
 def test_forward_windows_large_logits_fp16():
@@ -198,7 +204,7 @@ def test_forward_windows_large_logits_fp16():
     torch.cuda.synchronize()
     assert _native.read_status(torch.device(DEV)) == 0
     z_ref, _ = orc.tdp_forward(*(t.float() for t in (q, k1, k2, v1, v2)), 1 / 8, True, *windows)
-    assert float((o.float().cpu() - z_ref).abs().max()) <= 1e-2
+    assert_close("o", o.cpu(), z_ref, dtype)
 
 
 @pytest.mark.parametrize("D", [64, 128])
@@ -218,11 +224,10 @@ def test_backward_windows_match_oracle(windows, D):
     assert _native.read_status(torch.device(DEV)) == 0, "a bounded barrier wait ran out"
     f = [x.float() for x in (q, k1, k2, v1, v2)]
     g_ref = orc.tdp_backward(*f, dz.float(), alpha, True, *windows)
+    # windows (0, 0, 0, 0): every query attends the single pair (q, q), so dQ, dK1 and dK2 are exactly zero and the
+    # oracle's values for them are fp32 rounding noise (~1e-8, against ~1e-3 for the other window sets)
     for name, leaf, ref in zip(("dq", "dk1", "dk2", "dv1", "dv2"), leaves, g_ref):
-        g = leaf.grad.float().cpu()
-        assert torch.isfinite(g).all(), name
-        err, mag = float((g - ref).abs().max()), float(ref.abs().max())
-        assert err <= TOL[dtype] * max(1.0, mag), (name, err, mag)
+        assert_close(name, leaf.grad.cpu(), ref, dtype, zero_below=1e-6 if windows == (0, 0, 0, 0) else 0.0)
 
 
 @pytest.mark.parametrize("windows", [(64, 150, 30, 10), (8, 8, 4, 4)])
@@ -238,7 +243,7 @@ def test_windows_with_query_shards(windows):
     o2, lse2 = torch.zeros_like(o), torch.zeros_like(lse)
     for rem in range(4):
         _native.tdp_fwd(*t, o2, lse2, alpha, True, *windows, q_mod=4, q_rem=rem)
-    assert float((o2.float() - o.float()).abs().max()) <= 1e-2
+    assert_close("o (shards vs whole)", o2, o, torch.bfloat16)
     assert float((lse2 - lse).abs().max()) <= 1e-3
     full = [torch.empty_like(t[0]) for _ in range(5)]
     _native.tdp_bwd(*t, o, do, lse, *full, alpha, True, *windows)
@@ -256,7 +261,7 @@ def test_windows_with_query_shards(windows):
     torch.cuda.synchronize()
     assert _native.read_status(torch.device(DEV)) == 0
     for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), [dq] + outs, full):
-        assert float((a.float() - b.float()).abs().max()) <= 2e-2 * max(1.0, float(b.float().abs().max())), name
+        assert_close(name + " (shards vs whole)", a, b, torch.bfloat16)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -274,9 +279,9 @@ def test_forward_with_and_without_the_score_bound(dtype):
         torch.cuda.synchronize()
         assert _native.read_status(torch.device(DEV)) == 0
         outs.append((o.float(), lse))
-    assert float((outs[0][0] - outs[1][0]).abs().max()) <= 1e-2
+    assert_close("o (score bound vs two-pass)", outs[0][0], outs[1][0], dtype)
     assert float((outs[0][1] - outs[1][1]).abs().max()) <= 1e-3
     z_ref, lse_ref = orc.tdp_forward(*[x.float() for x in (q, k1, k2, v1, v2)], alpha, True)
     for o, lse in outs:
-        assert float((o.cpu() - z_ref).abs().max()) <= 2e-2
-        assert float((lse.cpu() - lse_ref).abs().max()) <= 2e-2
+        assert_close("o", o.cpu(), z_ref, dtype)
+        assert float((lse.cpu() - lse_ref).abs().max()) <= 5e-3

@@ -90,11 +90,10 @@ def test_16bit_forward_backward_small(dtype, tol, force_simt):
                       causal=True, convert_to_float32=force_simt)
     z_ref, _ = orc.tdp_forward(*(x.float() for x in (q, k1, k2, v1, v2)), scale, True)
     g_ref = orc.tdp_backward(*(x.float() for x in (q, k1, k2, v1, v2, dz)), scale, True)
-    assert (out.float() - z_ref).abs().max() <= tol
+    assert (out.float() - z_ref).abs().max() <= tol * float(z_ref.abs().max())
     for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), grads, g_ref):
-        # gradients of sums over T rows are O(10): scale the absolute bound by their magnitude
-        bound = tol * max(1.0, float(b.abs().max()))
-        assert (a.float() - b).abs().max() <= bound, name
+        # every gradient is bounded against its own magnitude
+        assert (a.float() - b).abs().max() <= tol * float(b.abs().max()), name
 
 
 def test_rejects_mismatched_shapes():

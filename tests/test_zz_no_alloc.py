@@ -41,10 +41,14 @@ def test_noalloc_forward_matches_workspace_forward_twice(shape, dtype):
         _native.tdp_fwd_noalloc(*t, o, lse, alpha, True, None, None, None, None)
         torch.cuda.synchronize()
         assert _native.read_status(torch.device(DEV)) == 0
-        # same kernels on the same inputs: the tolerance of the 16-bit parity tests is far more than needed
-        tol = {torch.bfloat16: 2e-2, torch.float16: 5e-3, torch.float32: 2e-5}[dtype]
-        assert float((o.float() - o_ref.float()).abs().max()) <= tol, f"call {call}"
-        assert float((lse - lse_ref).abs().max()) <= tol, f"call {call}"
+        # same kernels on the same inputs.  The tensor-core forward has no atomics: identical results.  The CUDA-core
+        # forward (the fp32 case) merges partial rows with fp32 atomic adds, whose order is not fixed: last-bit noise.
+        if dtype == torch.float32:
+            assert float((o - o_ref).abs().max()) <= 1e-6 * float(o_ref.abs().max()), f"call {call}"
+            assert float((lse - lse_ref).abs().max()) <= 1e-6 * float(lse_ref.abs().max()), f"call {call}"
+        else:
+            assert torch.equal(o, o_ref), f"call {call}: max diff {float((o.float() - o_ref.float()).abs().max())}"
+            assert torch.equal(lse, lse_ref), f"call {call}: max diff {float((lse - lse_ref).abs().max())}"
 
 
 def test_noalloc_rejects_problems_beyond_the_builtin_scratch():
