@@ -28,9 +28,12 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-for _p in (ROOT, os.path.join(ROOT, "flash-3-way-attention_b200")):
-    if _p not in sys.path:
-        sys.path.insert(0, _p)
+if not os.environ.get("TRITT_BENCH_REFERENCE_WORKER"):
+    # (the child process that times the reference's own kernels must import the reference's package of the same
+    #  name instead: see reference_kernel_worker)
+    for _p in (ROOT, os.path.join(ROOT, "flash-3-way-attention_b200")):
+        if _p not in sys.path:
+            sys.path.insert(0, _p)
 
 import torch  # noqa: E402
 
@@ -151,32 +154,69 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def _timed(fn, iters=5):
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
 def other_workloads(dev):
     """Short CUDA-event timings of the other benchmark configurations on one GPU (not part of the headline
-    value): config 2 forward, the reference's banded forward case, config 3 (dot-product-sum) forward+backward."""
+    value): config 2 forward, the shapes of the reference's own forward benchmark (b200/bench_b200.py there:
+    2 x 8 x {512, 1024} x 64 fp16 full windows, 2 x 8 x 2048 x 64 with windows 128/128/32/32), narrow bands,
+    a non-causal case, and config 3 (dot-product-sum) forward+backward."""
     from flash_trittention import flash_trittention
     from flash_trittention.dot_product_sum.trittention_triton import TrittentionTriton
-
-    def timed(fn, iters=5):
-        fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / iters
 
     out = {}
     t = [x.to(dev) for x in _make_inputs(4, 8, 512, 64, 0.5, 2, torch.bfloat16)[:5]]
     with torch.no_grad():
-        ms = timed(lambda: flash_trittention(*t, 1 / 64, None, None, None, None, True))
+        ms = _timed(lambda: flash_trittention(*t, 1 / 64, None, None, None, None, True))
     out["tdp_fwd_4x8x512x64_bf16"] = {"ms": ms, "tflops": _flops(4, 8, 512, 64, "fwd") / ms / 1e9}
+    for T in (512, 1024):
+        ins = [x.to(dev) for x in _make_inputs(2, 8, T, 64, 1.0, 3, torch.float16)]
+        with torch.no_grad():
+            ms = _timed(lambda: flash_trittention(*ins[:5], 1 / 8, None, None, None, None, True))
+        out[f"tdp_fwd_2x8x{T}x64_fp16"] = {"ms": ms, "tflops": _flops(2, 8, T, 64, "fwd") / ms / 1e9}
+        if T == 512:
+            def tdp_step():
+                leaves = [x.detach().requires_grad_(True) for x in ins[:5]]
+                flash_trittention(*leaves, 1 / 8, None, None, None, None, True).backward(ins[5])
+
+            ms = _timed(tdp_step)
+            out["tdp_fwd_bwd_2x8x512x64_fp16"] = {"ms": ms, "tflops": _flops(2, 8, 512, 64) / ms / 1e9}
+            # not causal: every (q, j, k) triple is attended, T^3 per head; the kernels execute exactly the
+            # algorithmic products forward (T is a multiple of the 128-wide tiles) and 8 for 6 backward
+            with torch.no_grad():
+                ms = _timed(lambda: flash_trittention(*ins[:5], 1 / 8, None, None, None, None, False))
+            fl = 4.0 * 64 * 2 * 8 * T ** 3
+            out["tdp_fwd_2x8x512x64_fp16_noncausal"] = {"ms": ms, "tflops": fl / ms / 1e9,
+                                                         "executed_over_algorithmic_flops": 1.0}
+
+            def nc_step():
+                leaves = [x.detach().requires_grad_(True) for x in ins[:5]]
+                flash_trittention(*leaves, 1 / 8, None, None, None, None, False).backward(ins[5])
+
+            ms = _timed(nc_step, iters=3)
+            out["tdp_fwd_bwd_2x8x512x64_fp16_noncausal"] = {"ms": ms, "tflops": 4 * fl / ms / 1e9,
+                                                             "executed_over_algorithmic_flops": (4 + 16) / 16.0}
     t = [x.to(dev) for x in _make_inputs(2, 8, 2048, 64, 1.0, 3, torch.float16)[:5]]
     with torch.no_grad():
-        ms = timed(lambda: flash_trittention(*t, 1 / 8, 32, 32, 128, 128, True))
-    out["tdp_fwd_2x8x2048x64_fp16_windows_128_128_32_32"] = {"ms": ms}
+        ms = _timed(lambda: flash_trittention(*t, 1 / 8, 32, 32, 128, 128, True))
+        out["tdp_fwd_2x8x2048x64_fp16_windows_128_128_32_32"] = {"ms": ms}
+        ms = _timed(lambda: flash_trittention(*t, 1 / 8, 4, 4, 8, 8, True))
+        out["tdp_fwd_2x8x2048x64_fp16_windows_8_8_4_4"] = {"ms": ms}
+    t = [x.to(dev) for x in _make_inputs(2, 8, 8192, 64, 1.0, 5, torch.float16)[:5]]
+    with torch.no_grad():
+        ms = _timed(lambda: flash_trittention(*t, 1 / 8, 32, 32, 128, 128, True), iters=3)
+    out["tdp_fwd_2x8x8192x64_fp16_windows_128_128_32_32"] = {"ms": ms}
+    del t
     ins = [x.to(dev) for x in _make_inputs(2, 8, 1024, 64, 1.0, 4, torch.float16)]
     mod = TrittentionTriton(causal=True, softmax_scale=1 / 8, k_diff=1024)
 
@@ -185,8 +225,126 @@ def other_workloads(dev):
         o, _ = mod(*leaves)
         o.backward(ins[5])
 
-    out["dps_fwd_bwd_2x8x1024x64_fp16"] = {"ms": timed(dps_step)}
+    out["dps_fwd_bwd_2x8x1024x64_fp16"] = {"ms": _timed(dps_step, iters=20)}
+    with torch.no_grad():
+        out["dps_fwd_2x8x1024x64_fp16"] = {"ms": _timed(lambda: mod(*ins[:5]), iters=20)}
     return out
+
+
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def reference_kernel_worker():
+    """Runs in a child process whose import path holds the unmodified reference package (installed from its own
+    pyproject into baseline/_ref, which is not part of the repository's history) and NOT this repository's package of
+    the same name: times the reference's Triton kernels on this GPU on the shapes of its own forward benchmark
+    (b200/bench_b200.py:107-150 there) and prints one JSON object."""
+    import triton.testing as tt
+    from b200.flash_trittention_b200 import flash_trittention_b200
+    from flash_trittention.triple_dot_product.flash_trittention import flash_trittention as ref_ft
+
+    dev = torch.device("cuda:0")
+    res = {"triton": __import__("triton").__version__}
+
+    def bench(fn, rep=60):
+        return float(tt.do_bench(fn, warmup=10, rep=rep))
+
+    for T, win, label in ((512, None, "full"), (1024, None, "full"), (2048, (128, 128, 32, 32), "windows_128_128_32_32")):
+        ins = [x.to(dev) for x in _make_inputs(2, 8, T, 64, 1.0, 3, torch.float16)]
+        w = win or (T, T, T, T)
+        kw = dict(softmax_scale=1 / 8, k1_window=w[0], k2_window=w[1], kk_left=w[2], kk_right=w[3], causal=True)
+        with torch.no_grad():
+            a = ref_ft(*ins[:5], **kw)
+            b = flash_trittention_b200(*ins[:5], **kw)
+            res[f"fwd_2x8x{T}x64_fp16_{label}"] = {
+                "generic_ms": bench(lambda: ref_ft(*ins[:5], **kw)),
+                "b200_ms": bench(lambda: flash_trittention_b200(*ins[:5], **kw)),
+                "generic_vs_b200_max_abs_diff": float((a.float() - b.float()).abs().max())}
+        if T == 512:
+            def step():
+                leaves = [x.detach().requires_grad_(True) for x in ins[:5]]
+                ref_ft(*leaves, **kw).backward(ins[5])
+
+            step()
+            torch.cuda.synchronize()
+            res["fwd_bwd_2x8x512x64_fp16_full"] = {"generic_ms": _timed(step, iters=3)}
+    print("REFJSON " + json.dumps(res), flush=True)
+
+
+def reference_kernel_timings(timeout_s=420):
+    """Times the reference's own GPU kernels beside ours (one GPU).  Returns a dict, or a one-line reason."""
+    if not os.path.isdir(os.path.join(REF_DIR, "flash_trittention")):
+        return {"unavailable": "reference tree not on GPU box (baseline/_ref is absent)"}
+    env = dict(os.environ)
+    env["PYTHONPATH"] = REF_DIR
+    env["TRITT_BENCH_REFERENCE_WORKER"] = "1"
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--reference-kernel-worker"], env=env,
+                           capture_output=True, text=True, timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"reference kernels did not finish within {timeout_s} s"}
+    for ln in r.stdout.splitlines():
+        if ln.startswith("REFJSON "):
+            return json.loads(ln[8:])
+    tail = (r.stderr or r.stdout).strip().splitlines()[-1:] or ["no output"]
+    return {"unavailable": f"reference kernels failed here (exit {r.returncode}): {tail[0][:200]}"}
+
+
+def config5(dev, world, rank):
+    """BASELINE config 5 (B=1, N=4, T=4096, D=64, bf16, causal, alpha = 1/D): on one GPU the plain entry point, on
+    several the query-row-sharded path (interleaved rows, one NCCL all-reduce of the fp32 key-side partial sums,
+    all-gathers of the output and dQ rows).  3 steps after 2 warm-ups, CUDA events, max over ranks; the all-reduce
+    of a buffer of the partial sums' size is also timed by itself."""
+    import torch.distributed as dist
+
+    from flash_trittention import flash_trittention
+    from flash_trittention.parallel import flash_trittention_query_sharded
+
+    B, N, T, D = 1, 4, 4096, 64
+    ins = [x.to(dev) for x in _make_inputs(B, N, T, D, 0.5, 11, torch.bfloat16)]
+
+    def step():
+        leaves = [x.detach().requires_grad_(True) for x in ins[:5]]
+        if world > 1:
+            out = flash_trittention_query_sharded(*leaves, 1.0 / D, True)
+        else:
+            out = flash_trittention(*leaves, 1.0 / D, None, None, None, None, True)
+        out.backward(ins[5])
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        sync()
+        ms = e0.elapsed_time(e1) / n
+        if world > 1:
+            tt = torch.tensor([ms], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        return ms
+
+    for _ in range(2):
+        step()
+    ms = timed(step, 3)
+    res = {"ms": ms, "tflops": _flops(B, N, T, D) / ms / 1e9, "n_gpus": world,
+           "path": "flash_trittention_query_sharded" if world > 1 else "flash_trittention"}
+    if world > 1:
+        buf = torch.zeros(4 * B * N * T * D, device=dev)
+        for _ in range(2):
+            dist.all_reduce(buf)
+        ar = timed(lambda: dist.all_reduce(buf), 5)
+        res["allreduce_ms"] = ar
+        res["allreduce_bytes"] = buf.numel() * 4
+        res["allreduce_share_of_step"] = ar / ms
+    return res
 
 
 def run_ours(args):
@@ -290,6 +448,8 @@ def run_ours(args):
         ms_e2e = timed(step_e2e, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     status = _native.read_status(dev)
+    # config 5 after the headline measurement (every rank takes part in its collectives)
+    c5 = None if args.skip_cpu else config5(dev, world, rank)
 
     if rank != 0:
         if world > 1:
@@ -338,6 +498,9 @@ def run_ours(args):
     }
     if world == 1 and not args.skip_cpu:
         line["other_workloads"] = other_workloads(dev)
+        line["other_workloads"]["reference_kernels_same_gpu"] = reference_kernel_timings()
+    if c5 is not None:
+        line.setdefault("other_workloads", {})["c5_query_sharded" if world > 1 else "c5_one_gpu"] = c5
     if cpu_v is not None:
         line["cpu_baseline"] = {"value": cpu_v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                                 "sample": cpu_sample}
@@ -359,11 +522,19 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="profiler captures: no CPU baseline sample")
     ap.add_argument("--only-other", action="store_true",
                     help="profiler captures: only the short timings of the other configurations (one GPU)")
+    ap.add_argument("--with-reference-kernels", action="store_true",
+                    help="with --only-other: also time the reference's Triton kernels from baseline/_ref")
+    ap.add_argument("--reference-kernel-worker", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
-    if args.only_other:
+    if args.reference_kernel_worker:
+        reference_kernel_worker()
+    elif args.only_other:
         dev = torch.device("cuda:0")
         torch.cuda.set_device(dev)
-        print(json.dumps({"other_workloads": other_workloads(dev)}))
+        ow = other_workloads(dev)
+        if args.with_reference_kernels:
+            ow["reference_kernels_same_gpu"] = reference_kernel_timings()
+        print(json.dumps({"other_workloads": ow}))
     elif args.impl == "reference":
         run_reference(args)
     else:

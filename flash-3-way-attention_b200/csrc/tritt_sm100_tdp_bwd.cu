@@ -385,8 +385,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       }
       if (!sm_sync()) { alive = false; break; }
       const float Dq = misc[0] + misc[1] + misc[2] + misc[3];
-      // a query that attends a single pair has P = 1 and a score gradient of exactly zero (TdpMask::single_pair)
-      const bool single = TdpMask{p.causal, T, p.k1w, p.k2w, p.kkl, p.kkr}.single_pair(q);
       const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e;
       const float scale2 = p.alpha * kLog2e;
 
@@ -474,15 +472,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 #pragma unroll
             for (int sc = 0; sc < CW / 32; ++sc) tmem_ld32(tDP + sc * 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[sc * 32]));
             tmem_wait_ld();
-            if (single) {
 #pragma unroll
-              for (int i = 0; i < CW / 2; ++i) dk[i] = 0u;
-            } else {
-#pragma unroll
-              for (int i = 0; i < CW; i += 2) {
-                const float2 pp = unpack2<T16>(pk[i >> 1]);
-                dk[i >> 1] = pack2<T16>(pp.x * (__uint_as_float(dp[i]) - Dq), pp.y * (__uint_as_float(dp[i + 1]) - Dq));
-              }
+            for (int i = 0; i < CW; i += 2) {
+              const float2 pp = unpack2<T16>(pk[i >> 1]);
+              dk[i >> 1] = pack2<T16>(pp.x * (__uint_as_float(dp[i]) - Dq), pp.y * (__uint_as_float(dp[i + 1]) - Dq));
             }
           }
           tmem_st(tDP, dk);  // dS -> first half of this warpgroup's dP columns
@@ -522,6 +515,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       const CUtensorMap* tmDY = role == 0 ? &tmDV2 : &tmDSV1;
       const float* qv = vec + (item_count & 1) * 2 * D;
       const float* dov = qv + D;
+      // A query that attends a single pair has P = 1 and a score gradient of exactly zero (TdpMask::single_pair):
+      // what G holds for it is P (dP - Dq) with the two terms equal only up to the 16-bit rounding of the stored
+      // output, so G is dropped (dQ = 0, nothing added to dK1 / dK2) instead of being folded.
+      const bool single = TdpMask{p.causal, T, p.k1w, p.k2w, p.kkl, p.kkr}.single_pair(q);
       if (role == 0) {
         if (row < D) dq_acc[row] = 0.f;
         if (!fold_sync()) { alive = false; break; }
@@ -540,7 +537,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           const int h0 = (is_u ? pc : pc - D / 32) * 32;
           // role 0, G pieces: this row's X values for the dQ product (issued early to hide the latency)
           uint4 xr[4];
-          const bool want_dq = !is_u && role == 0;
+          const bool want_dq = !is_u && role == 0 && !single;
           if (want_dq) {
 #pragma unroll
             for (int i4 = 0; i4 < 4; ++i4)
@@ -587,7 +584,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           fence_async_smem();
           __syncwarp();
           // (rows beyond the query carry zeros: a warp whose 32 rows are all beyond it has nothing to add)
-          if (lane == 0 && warp_rows_live) {
+          if (lane == 0 && warp_rows_live && (is_u || !single)) {
             tma_reduce_add_3d(is_u ? tmDY : tmDX, slot, h0, xt * 128 + wq * 32, bh);
             bulk_commit();
           }
