@@ -134,6 +134,9 @@ int sm100_tdp_bwd(const TdpArgs& a);
 size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype);
 size_t sm100_tdp_bwd_workspace(int B, int N, int T, int D);
 size_t sm100_tdp_fwd_optional_workspace(int B, int N, int T, int D, int dtype);
+// forward kernel for causal masks with a narrow (j, k) band (tiles of four queries x 32 K2 rows)
+bool sm100_tdp_fwd_band_applies(int T, const TdpMask& m);
+int sm100_tdp_fwd_band(const TdpArgs& a, const void* sv1, const float* k1n);
 
 // Two-way soft-max attention forward on the tensor cores (16-bit operands [BN, T, D], head dimension 64 or 128):
 // out[r] = softmax_c(alpha x[r].k[c] + bias[c]) v[c] over the columns with (not causal, or c <= r <= c + win).

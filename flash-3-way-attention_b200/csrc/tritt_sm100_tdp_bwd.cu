@@ -89,6 +89,20 @@ struct BwdBarriers {
 };
 
 
+// fp16 only: the recomputed probabilities of a query that attends n pairs are ~1/n, which for late rows lies below
+// fp16's normal range (6e-5; 1/n = 2e-7 at q = 2048).  P and dS are therefore formed times 2^e, e = min(10, log2 of
+// the attended pairs' count bound), and the fold warpgroup divides it out of G and U.  2^10 keeps a probability of 1
+// times a dP - Dq of up to 64 finite.  bf16 has fp32's exponent range and needs none of this (e = 0).
+template <typename T16>
+__device__ __forceinline__ int prob_shift(int q, int causal, int T, int k1w, int k2w) {
+  if constexpr (std::is_same<T16, __half>::value) {
+    const int n1 = causal ? min(q, k1w) + 1 : T, n2 = causal ? min(q, k2w) + 1 : T;
+    const int e = (31 - __clz(n1)) + (31 - __clz(n2));
+    return min(10, e);
+  }
+  return 0;
+}
+
 template <int D, typename T16, int NSW>
 __global__ void __launch_bounds__(BwdThreads<NSW>::kTotal, 1)
 tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__ CUtensorMap tmK2,
@@ -385,7 +399,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       }
       if (!sm_sync()) { alive = false; break; }
       const float Dq = misc[0] + misc[1] + misc[2] + misc[3];
-      const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e;
+      // (minus the fp16 range shift: P below is the probability times 2^e)
+      const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e - (float)prob_shift<T16>(q, p.causal, T, p.k1w, p.k2w);
       const float scale2 = p.alpha * kLog2e;
 
       for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
@@ -519,6 +534,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       // what G holds for it is P (dP - Dq) with the two terms equal only up to the 16-bit rounding of the stored
       // output, so G is dropped (dQ = 0, nothing added to dK1 / dK2) instead of being folded.
       const bool single = TdpMask{p.causal, T, p.k1w, p.k2w, p.kkl, p.kkr}.single_pair(q);
+      // undoes the fp16 range shift of P and dS (1 for bf16)
+      const float unshift = exp2f(-(float)prob_shift<T16>(q, p.causal, T, p.k1w, p.k2w));
+      const float alpha_u = p.alpha * unshift;
       if (role == 0) {
         if (row < D) dq_acc[row] = 0.f;
         if (!fold_sync()) { alive = false; break; }
@@ -552,7 +570,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           float v[32];
           {
             const float4* mul = reinterpret_cast<const float4*>((is_u ? dov : qv) + h0);
-            const float sc = is_u ? 1.f : p.alpha;
+            const float sc = is_u ? unshift : alpha_u;
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               const float4 m = mul[i4];
@@ -595,8 +613,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const float2 f = unpack2<T16>(wx[e]);
-                v[i4 * 8 + 2 * e] = p.alpha * __uint_as_float(g[i4 * 8 + 2 * e]) * f.x;
-                v[i4 * 8 + 2 * e + 1] = p.alpha * __uint_as_float(g[i4 * 8 + 2 * e + 1]) * f.y;
+                v[i4 * 8 + 2 * e] = alpha_u * __uint_as_float(g[i4 * 8 + 2 * e]) * f.x;
+                v[i4 * 8 + 2 * e + 1] = alpha_u * __uint_as_float(g[i4 * 8 + 2 * e + 1]) * f.y;
               }
             }
             const float colsum = warp_transpose_sum(v, lane);

@@ -678,28 +678,41 @@ __global__ void k1_norm2_max_kernel(const T16* __restrict__ k1, float* __restric
   if (lane == 0) atomicMax(reinterpret_cast<int*>(out + r / T), __float_as_int(s));
 }
 
-template <int D, typename T16>
-int launch_fwd(const TdpArgs& a) {
-  using Cfg = FwdCfg<D>;
+// What both forward kernels need before they start: SiLU(V1) in the inputs' type at the head of the workspace and,
+// when the workspace has the optional tail, the per-head largest squared K1 row norm (for the score bound).
+template <typename T16>
+int prepare_fwd(const TdpArgs& a, T16** sv1_out, float** k1n_out) {
   const int BN = a.B * a.N;
   const size_t n = (size_t)BN * a.T * a.D;
   T16* sv1 = (T16*)a.workspace;
   silu_kernel<T16><<<(unsigned)((n / 8 + 255) / 256 + 1), 256, 0, a.stream>>>((const T16*)a.v1, sv1, n);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
-  // Optional tail of the workspace: per-head largest squared K1 row norm, for the kernel's score bound.
   float* k1n = nullptr;
   const size_t tail = align_up(n * 2, 256);
   if (a.workspace_bytes >= tail + (size_t)BN * sizeof(float)) {
     k1n = reinterpret_cast<float*>((char*)a.workspace + tail);
     TRITT_CUDA_OK(cudaMemsetAsync(k1n, 0, (size_t)BN * sizeof(float), a.stream));
     const size_t rows = (size_t)BN * a.T;
-    k1_norm2_max_kernel<T16><<<(unsigned)((rows + 7) / 8), 256, 0, a.stream>>>((const T16*)a.k1, k1n, rows, a.T, D);
+    k1_norm2_max_kernel<T16><<<(unsigned)((rows + 7) / 8), 256, 0, a.stream>>>((const T16*)a.k1, k1n, rows, a.T, a.D);
     count_launch();
     TRITT_CUDA_OK(cudaGetLastError());
   }
+  *sv1_out = sv1;
+  *k1n_out = k1n;
+  return 0;
+}
+
+template <int D, typename T16>
+int launch_fwd(const TdpArgs& a) {
+  using Cfg = FwdCfg<D>;
+  const int BN = a.B * a.N;
+  T16* sv1 = nullptr;
+  float* k1n = nullptr;
+  int rc = prepare_fwd<T16>(a, &sv1, &k1n);
+  if (rc) return rc;
+  if (sm100_tdp_fwd_band_applies(a.T, a.mask)) return sm100_tdp_fwd_band(a, sv1, k1n);
   CUtensorMap tmK1, tmK2, tmSV1;
-  int rc;
   if ((rc = make_tmap_3d(&tmK1, a.k1, 2, D, a.T, BN, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tmSV1, sv1, 2, D, a.T, BN, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tmK2, a.k2, 2, D, a.T, BN, 64, 128))) return rc;
@@ -761,8 +774,8 @@ size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype) {
 }
 
 int sm100_tdp_fwd(const TdpArgs& a) {
-  // the two queries of a pair must fall in the same 128-row block
-  if (a.q_mod < 1 || a.q_mod > 64 || (a.q_mod & (a.q_mod - 1))) {
+  // general kernel: the two queries of a pair must fall in the same 128-row block (the band kernel has no such rule)
+  if (!sm100_tdp_fwd_band_applies(a.T, a.mask) && (a.q_mod < 1 || a.q_mod > 64 || (a.q_mod & (a.q_mod - 1)))) {
     set_error("tensor-core path needs a power-of-two query shard count <= 64 (got %d)", a.q_mod);
     return -30;
   }
