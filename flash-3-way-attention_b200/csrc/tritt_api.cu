@@ -112,6 +112,7 @@ const char* tritt_last_error(void) { return get_error(); }
 int tritt_tdp_path(int op, int T, int D, int dtype, int causal, int k1_window, int k2_window, int kk_left,
                    int kk_right, int flags) {
   TdpMask m = make_tdp_mask(causal, T, k1_window, k2_window, kk_left, kk_right);
+  if (tdp_wide_applies(op, T, D, dtype, m, flags)) return TRITT_PATH_TCGEN05;
   return use_sm100(op, T, D, dtype, m, flags) ? TRITT_PATH_TCGEN05 : TRITT_PATH_SIMT;
 }
 
@@ -121,15 +122,25 @@ int tritt_dps_path(int T, int D, int dtype, int k_diff, int flags) {
 }
 
 size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype) {
+  return tritt_workspace_bytes_flags(op, B, N, T, D, dtype, 0);
+}
+
+size_t tritt_workspace_bytes_flags(int op, int B, int N, int T, int D, int dtype, int flags) {
   if (B <= 0 || N <= 0 || T <= 0 || D <= 0) return 0;
   size_t a = 0, b = 0;
   switch (op) {
     case TRITT_OP_TDP_FWD:
-    case TRITT_OP_TDP_BWD:
+    case TRITT_OP_TDP_BWD: {
       a = simt_tdp_workspace(op, B, N, T, D, dtype);
       b = sm100_tdp_workspace(op, B, N, T, D, dtype);
       if (op == TRITT_OP_TDP_FWD && b) b += sm100_tdp_fwd_optional_workspace(B, N, T, D, dtype);
+      const TdpMask any = make_tdp_mask(1, T, T, T, T, T);
+      if (tdp_wide_applies(op, T, D, dtype, any, flags)) {
+        const size_t w = tdp_wide_workspace(op, B, N, T, D);
+        b = w > b ? w : b;
+      }
       break;
+    }
     case TRITT_OP_DPS_FWD:
     case TRITT_OP_DPS_BWD:
       a = dps_workspace(op, B, N, T, D, dtype);
@@ -141,6 +152,17 @@ size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype) {
 }
 
 size_t tritt_tdp_bwd_partials_offset(int, int, int, int, int) { return 0; }
+
+// Bytes of scratch the forward cannot run without on the kernel family it will take (the optional tail of the
+// tensor-core forward is not counted).  Shared with the allocation-free entry point.
+size_t tritt_tdp_fwd_min_workspace(int B, int N, int T, int D, int dtype, int causal, int k1_window, int k2_window,
+                                   int kk_left, int kk_right, int flags) {
+  const TdpMask m = make_tdp_mask(causal, T, k1_window, k2_window, kk_left, kk_right);
+  if (tdp_wide_applies(TRITT_OP_TDP_FWD, T, D, dtype, m, flags))
+    return tdp_wide_workspace(TRITT_OP_TDP_FWD, B, N, T, D) - sm100_tdp_fwd_optional_workspace(B, N, T, D, TRITT_F16);
+  if (use_sm100(TRITT_OP_TDP_FWD, T, D, dtype, m, flags)) return sm100_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
+  return simt_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
+}
 
 int tritt_tdp_fwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, void* o,
                   float* lse, int B, int N, int T, int D, int dtype, float alpha, int causal, int k1_window,
@@ -160,10 +182,11 @@ int tritt_tdp_fwd(const void* q, const void* k1, const void* k2, const void* v1,
   a.q_mod = q_mod; a.q_rem = q_rem;
   a.workspace = workspace; a.workspace_bytes = workspace_bytes;
   a.status_word = status_word; a.flags = flags; a.stream = (cudaStream_t)stream;
+  const bool wide = tdp_wide_applies(TRITT_OP_TDP_FWD, T, D, dtype, a.mask, flags);
   const bool fast = use_sm100(TRITT_OP_TDP_FWD, T, D, dtype, a.mask, flags);
-  const size_t need = fast ? sm100_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype)
-                           : simt_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
+  const size_t need = tritt_tdp_fwd_min_workspace(B, N, T, D, dtype, causal, k1_window, k2_window, kk_left, kk_right, flags);
   if ((rc = check_ws(need, workspace, workspace_bytes))) return rc;
+  if (wide) return tdp_wide_fwd(a);
   return fast ? sm100_tdp_fwd(a) : simt_tdp_fwd(a);
 }
 
@@ -192,10 +215,13 @@ int tritt_tdp_bwd(const void* q, const void* k1, const void* k2, const void* v1,
   a.q_mod = q_mod; a.q_rem = q_rem;
   a.workspace = workspace; a.workspace_bytes = workspace_bytes;
   a.status_word = status_word; a.flags = flags; a.stream = (cudaStream_t)stream;
+  const bool wide = tdp_wide_applies(TRITT_OP_TDP_BWD, T, D, dtype, a.mask, flags);
   const bool fast = use_sm100(TRITT_OP_TDP_BWD, T, D, dtype, a.mask, flags);
-  const size_t need = fast ? sm100_tdp_workspace(TRITT_OP_TDP_BWD, B, N, T, D, dtype)
-                           : simt_tdp_workspace(TRITT_OP_TDP_BWD, B, N, T, D, dtype);
+  const size_t need = wide   ? tdp_wide_workspace(TRITT_OP_TDP_BWD, B, N, T, D)
+                      : fast ? sm100_tdp_workspace(TRITT_OP_TDP_BWD, B, N, T, D, dtype)
+                             : simt_tdp_workspace(TRITT_OP_TDP_BWD, B, N, T, D, dtype);
   if ((rc = check_ws(need, workspace, workspace_bytes))) return rc;
+  if (wide) return tdp_wide_bwd(a);
   return fast ? sm100_tdp_bwd(a) : simt_tdp_bwd(a);
 }
 

@@ -138,6 +138,12 @@ size_t sm100_tdp_fwd_optional_workspace(int B, int N, int T, int D, int dtype);
 bool sm100_tdp_fwd_band_applies(int T, const TdpMask& m);
 int sm100_tdp_fwd_band(const TdpArgs& a, const void* sv1, const float* k1n);
 
+// fp32 inputs, and bf16 inputs with TRITT_FLAG_WIDE_OPERANDS, on the tensor cores through fp16 operand copies
+bool tdp_wide_applies(int op, int T, int D, int dtype, const TdpMask& m, int flags);
+size_t tdp_wide_workspace(int op, int B, int N, int T, int D);
+int tdp_wide_fwd(const TdpArgs& a);
+int tdp_wide_bwd(const TdpArgs& a);
+
 // Two-way soft-max attention forward on the tensor cores (16-bit operands [BN, T, D], head dimension 64 or 128):
 // out[r] = softmax_c(alpha x[r].k[c] + bias[c]) v[c] over the columns with (not causal, or c <= r <= c + win).
 struct AttnTcArgs {

@@ -77,15 +77,13 @@ extern "C" int tritt_tdp_fwd_noalloc(const void* q, const void* k1, const void* 
                                      int* status_word, int flags, tritt_stream_t stream) {
   // The bytes the kernel family this call will run on cannot do without (the same choice tritt_tdp_fwd makes; the
   // optional tail that tritt_workspace_bytes adds is used when the scratch has room for it).
-  const bool tc = tritt_tdp_path(TRITT_OP_TDP_FWD, T, D, dtype, causal, k1_window, k2_window, kk_left, kk_right,
-                                 flags) == TRITT_PATH_TCGEN05;
-  const size_t need = tc ? tritt::sm100_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype)
-                         : tritt::simt_tdp_workspace(TRITT_OP_TDP_FWD, B, N, T, D, dtype);
+  const size_t need =
+      tritt_tdp_fwd_min_workspace(B, N, T, D, dtype, causal, k1_window, k2_window, kk_left, kk_right, flags);
   if (need > kNoAllocScratchBytes) {
     tritt::set_error(
         "tritt_tdp_fwd_noalloc: this problem needs %zu bytes of scratch, above the built-in maximum of %zu bytes "
-        "(16-bit inputs on the tensor-core path are limited to B*N*T*D <= %zu elements); use tritt_tdp_fwd with a "
-        "caller-provided workspace",
+        "(16-bit inputs on the tensor-core path are limited to B*N*T*D <= %zu elements, fp32 inputs there to a "
+        "seventh of that); use tritt_tdp_fwd with a caller-provided workspace",
         need, kNoAllocScratchBytes, kNoAllocScratchBytes / 2);
     return -42;
   }

@@ -16,14 +16,15 @@ LIB_PATH = os.path.join(_HERE, "libtritt_sm100.so")
 
 F32, F16, BF16 = 0, 1, 2
 OP_TDP_FWD, OP_TDP_BWD, OP_DPS_FWD, OP_DPS_BWD = 0, 1, 2, 3
-FLAG_FORCE_SIMT, FLAG_BWD_PARTIAL = 1, 2
+FLAG_FORCE_SIMT, FLAG_BWD_PARTIAL, FLAG_WIDE_OPERANDS = 1, 2, 4
 PATH_SIMT, PATH_TCGEN05 = 0, 1
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 # every symbol include/tritt.h declares
 SYMBOLS = (
-    "tritt_version", "tritt_kernel_launches", "tritt_last_error", "tritt_workspace_bytes", "tritt_tdp_path", "tritt_dps_path", "tritt_tdp_fwd",
+    "tritt_version", "tritt_kernel_launches", "tritt_last_error", "tritt_workspace_bytes", "tritt_workspace_bytes_flags",
+    "tritt_tdp_fwd_min_workspace", "tritt_tdp_path", "tritt_dps_path", "tritt_tdp_fwd",
     "tritt_tdp_bwd", "tritt_tdp_bwd_finalize", "tritt_tdp_bwd_partials_offset", "tritt_dps_fwd",
     "tritt_dps_bwd", "tritt_selftest_umma", "tritt_selftest_wait_expiry", "tritt_tdp_fwd_noalloc",
     "tritt_noalloc_scratch_bytes",
@@ -56,6 +57,10 @@ def lib():
                 L.tritt_last_error.restype = C.c_char_p
                 L.tritt_workspace_bytes.restype = sz
                 L.tritt_workspace_bytes.argtypes = [i] * 6
+                L.tritt_workspace_bytes_flags.restype = sz
+                L.tritt_workspace_bytes_flags.argtypes = [i] * 7
+                L.tritt_tdp_fwd_min_workspace.restype = sz
+                L.tritt_tdp_fwd_min_workspace.argtypes = [i] * 11
                 L.tritt_tdp_path.restype = i
                 L.tritt_tdp_path.argtypes = [i] * 10
                 L.tritt_dps_path.restype = i
@@ -101,6 +106,7 @@ def _check(rc: int, what: str):
 STATUS_BITS = {1: "self-test kernel", 2: "triple-dot-product forward", 4: "triple-dot-product backward",
                8: "shared memory of a tensor-core kernel was not 1024-byte aligned",
                16: "soft-max attention forward (dot-product-sum)", 32: "soft-max attention backward (dot-product-sum)",
+               64: "an input element beyond the fp16 operand range (65504) in an fp32 / wide-operand call",
                128: "wait-expiry self-test"}
 
 
@@ -153,12 +159,13 @@ def check_status(device=None, synchronize: bool = True) -> None:
         if v:
             t.zero_()
     if v:
-        raise TrittError(f"a kernel of an earlier call on cuda:{dev} gave up waiting on a barrier after its time "
-                         f"limit ({_describe(v)}); the results of that call are invalid")
+        raise TrittError(f"a kernel of an earlier call on cuda:{dev} reported a failure: gave up waiting on a barrier "
+                         f"after its time limit, or met unusable input ({_describe(v)}); the results of that call "
+                         "are invalid")
 
 
-def workspace(op: int, B: int, N: int, T: int, D: int, dtype: int, device) -> torch.Tensor:
-    nbytes = lib().tritt_workspace_bytes(op, B, N, T, D, dtype)
+def workspace(op: int, B: int, N: int, T: int, D: int, dtype: int, device, flags: int = 0) -> torch.Tensor:
+    nbytes = lib().tritt_workspace_bytes_flags(op, B, N, T, D, dtype, flags)
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
 
@@ -194,7 +201,7 @@ def tdp_fwd(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr, q_mod=
     check_status(q.device, synchronize=False)
     with torch.cuda.device(q.device):
         if ws is None:
-            ws = workspace(OP_TDP_FWD, B, N, T, D, dt, q.device)
+            ws = workspace(OP_TDP_FWD, B, N, T, D, dt, q.device, flags)
         rc = lib().tritt_tdp_fwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
                                  o.data_ptr(), lse.data_ptr(), B, N, T, D, dt, float(alpha), int(bool(causal)),
                                  _win(k1w, T), _win(k2w, T), _win(kkl, T), _win(kkr, T), q_mod, q_rem,
@@ -213,7 +220,7 @@ def tdp_bwd(q, k1, k2, v1, v2, o, do, lse, dq, dk1, dk2, dv1, dv2, alpha, causal
     check_status(q.device, synchronize=False)
     with torch.cuda.device(q.device):
         if ws is None:
-            ws = workspace(OP_TDP_BWD, B, N, T, D, dt, q.device)
+            ws = workspace(OP_TDP_BWD, B, N, T, D, dt, q.device, flags)
         rc = lib().tritt_tdp_bwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
                                  o.data_ptr(), do.data_ptr(), lse.data_ptr(), dq.data_ptr(), ptr(dk1), ptr(dk2),
                                  ptr(dv1), ptr(dv2), B, N, T, D, dt, float(alpha), int(bool(causal)),

@@ -38,7 +38,7 @@ class TrittentionTritonFunction(torch.autograd.Function):
         m = torch.empty(q.shape[:3], device=q.device, dtype=torch.float32)
         # convert_to_float32 asks for fp32 operands inside the kernels (reference trittention_triton.py:98-117
         # forwards it to its launches): the CUDA-core path computes in fp32 on every dtype
-        flags = _native.FLAG_FORCE_SIMT if convert_to_float32 else 0
+        flags = _native.FLAG_FORCE_SIMT if (convert_to_float32 or input_precision == "ieee") else 0
         _native.dps_fwd(q, k1, k2, v1, v2, o, m, softmax_scale, causal, k_diff, flags=flags)
         ctx.flags = flags
         ctx.causal = causal
@@ -85,7 +85,7 @@ class TrittentionTriton(nn.Module):
         16-bit inputs with a head dimension of 64 or 128 run on the tensor cores with 16-bit operands (the
         probabilities and ``Y*V2`` are rounded to the inputs' type, accumulation and soft-max state are fp32);
         ``convert_to_float32=True`` selects the fp32 CUDA-core kernels instead, as do fp32 inputs and other
-        head dimensions.  ``input_precision`` is accepted for interface parity and has no effect.
+        head dimensions, and ``input_precision="ieee"`` (the reference's name for exact fp32 dot products).
         """
         return TrittentionTritonFunction.apply(q, k1, k2, v1, v2, self.causal, self.softmax_scale, self.k_diff,
                                                self.convert_to_float32, self.input_precision)

@@ -54,7 +54,7 @@ def tdp_fwd(q: Tensor, k1: Tensor, k2: Tensor, v1: Tensor, v2: Tensor, softmax_s
     q, k1, k2, v1, v2 = (_native.aligned(t) for t in (q, k1, k2, v1, v2))
     o = torch.empty_like(q)
     lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
-    flags = _native.FLAG_FORCE_SIMT if convert_to_float32 else 0
+    flags = _native.FLAG_WIDE_OPERANDS if convert_to_float32 else 0
     _native.tdp_fwd(q, k1, k2, v1, v2, o, lse, softmax_scale, causal, k1_window, k2_window, kk_left, kk_right,
                     flags=flags)
     return o, lse
@@ -76,7 +76,7 @@ def tdp_bwd(q: Tensor, k1: Tensor, k2: Tensor, v1: Tensor, v2: Tensor, o: Tensor
     q, k1, k2, v1, v2, o, lse = (_native.aligned(t) for t in (q, k1, k2, v1, v2, o, lse))
     d_o = _native.aligned(d_o.to(q.dtype))
     grads = tuple(torch.empty_like(q) for _ in range(5))
-    flags = _native.FLAG_FORCE_SIMT if convert_to_float32 else 0
+    flags = _native.FLAG_WIDE_OPERANDS if convert_to_float32 else 0
     _native.tdp_bwd(q, k1, k2, v1, v2, o, d_o, lse, *grads, softmax_scale, causal, k1_window, k2_window, kk_left,
                     kk_right, flags=flags)
     return grads

@@ -38,7 +38,9 @@ def _validate(Q, K1, K2, V1, V2):
 class FlashTrittention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K1, K2, V1, V2, softmax_scale, kk_left, kk_right, k1_window, k2_window, causal,
-                convert_to_float32):
+                convert_to_float32, *extra):
+        # `extra`: at most one more positional argument, True for the exact-fp32 CUDA-core kernels
+        # (``input_precision="ieee"`` of the functional entry point); the reference's signature ends before it
         _validate(Q, K1, K2, V1, V2)
         seq_len = Q.shape[2]
         Q, K1, K2, V1, V2 = (_native.aligned(t) for t in (Q, K1, K2, V1, V2))
@@ -46,8 +48,13 @@ class FlashTrittention(torch.autograd.Function):
             seq_len, k1_window, k2_window, kk_left, kk_right)
         O = torch.empty_like(Q)
         lse = torch.empty(Q.shape[:3], dtype=torch.float32, device=Q.device)
-        # convert_to_float32 asks for fp32 operands inside the kernel: the CUDA-core path computes in fp32
-        flags = _native.FLAG_FORCE_SIMT if convert_to_float32 else 0
+        # convert_to_float32 asks for fp32 operands inside the kernel, which the reference then feeds to TF32 dot
+        # products: here bf16 inputs get operands of TF32's 11 significant bits (fp16 copies) on the tensor cores;
+        # fp16 inputs have them already, fp32 inputs always run that way
+        flags = _native.FLAG_WIDE_OPERANDS if convert_to_float32 else 0
+        if extra and extra[0]:
+            flags = _native.FLAG_FORCE_SIMT
+        ctx.n_extra = len(extra)
         _native.tdp_fwd(Q, K1, K2, V1, V2, O, lse, softmax_scale, causal, k1_window, k2_window, kk_left, kk_right,
                         flags=flags)
         ctx.save_for_backward(Q, K1, K2, V1, V2, O, lse)
@@ -67,7 +74,7 @@ class FlashTrittention(torch.autograd.Function):
         k1_window, k2_window, kk_left, kk_right = ctx.windows
         _native.tdp_bwd(Q, K1, K2, V1, V2, O, dO, lse, dq, dk1, dk2, dv1, dv2, ctx.softmax_scale, ctx.causal,
                         k1_window, k2_window, kk_left, kk_right, flags=ctx.flags)
-        return dq, dk1, dk2, dv1, dv2, None, None, None, None, None, None, None
+        return (dq, dk1, dk2, dv1, dv2, None, None, None, None, None, None, None) + (None,) * ctx.n_extra
 
 
 def flash_trittention(
@@ -92,10 +99,14 @@ def flash_trittention(
     is attended iff ``j <= q <= j + k1_window``, ``k <= q <= k + k2_window`` and
     ``k - kk_left <= j <= k + kk_right``; a window of ``None`` spans the sequence.
 
-    ``input_precision`` is accepted and ignored with a warning, as in the reference
-    (``flash_trittention.py:418-424``).
+    Precision: 16-bit inputs run with 16-bit tensor-core operands and fp32 accumulation; fp32 inputs (head dimension 64
+    or 128) and ``convert_to_float32=True`` on bf16 inputs run on the tensor cores with operands of 11 significant
+    bits, the precision of the TF32 dot products the reference feeds them to.  ``input_precision="ieee"`` selects
+    exact-fp32 arithmetic on the CUDA cores (much slower); any other value is accepted and ignored with a warning, as
+    the reference does for every value (``flash_trittention.py:418-424``).
     """
-    if input_precision is not None:
+    exact = input_precision == "ieee"
+    if input_precision is not None and not exact:
         warnings.warn(
             "flash_trittention: `input_precision` is currently unused and has no "
             f"effect (got {input_precision!r}); matmuls run at the kernel's default precision.",
@@ -107,5 +118,8 @@ def flash_trittention(
 
         return tdp_attention(q, k1, k2, v1, v2, softmax_scale, causal, k1_window, k2_window, kk_left, kk_right,
                              convert_to_float32)[0]
+    if exact:
+        return FlashTrittention.apply(q, k1, k2, v1, v2, softmax_scale, kk_left, kk_right, k1_window, k2_window, causal,
+                                      convert_to_float32, True)
     return FlashTrittention.apply(q, k1, k2, v1, v2, softmax_scale, kk_left, kk_right, k1_window, k2_window, causal,
                                   convert_to_float32)

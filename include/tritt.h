@@ -19,7 +19,8 @@
  *   - `status_word` (an int the GPU can address: device memory or page-locked host memory; may be NULL)
  *     is OR-ed with a non-zero code by a kernel whose bounded barrier wait ran out (1 tensor-core
  *     self-test, 2 / 4 triple-dot-product forward / backward, 8 misaligned shared memory, 16 / 32
- *     soft-max attention forward / backward of the dot-product-sum path, 128 wait-expiry self-test);
+ *     soft-max attention forward / backward of the dot-product-sum path, 128 wait-expiry self-test) or,
+ *     bit 64, by the fp16 operand conversion of an fp32 / wide-operand call that met an element beyond 65504;
  *     the caller zeroes and reads it.  A non-zero word means the results of that call are invalid;
  *   - window arguments (k1_window, k2_window, kk_left, kk_right, k_diff) are distances >= 0; a value
  *     >= T means "unlimited".  Negative values are refused with an argument error when `causal` is set
@@ -46,9 +47,15 @@ enum { TRITT_OP_TDP_FWD = 0, TRITT_OP_TDP_BWD = 1, TRITT_OP_DPS_FWD = 2, TRITT_O
 /* flags */
 enum {
   TRITT_FLAG_FORCE_SIMT = 1,  /* use the plain fp32 CUDA-core kernels even where the tensor-core path applies */
-  TRITT_FLAG_BWD_PARTIAL = 2  /* tritt_tdp_bwd: leave the fp32 key-side partial sums in the workspace and do not
+  TRITT_FLAG_BWD_PARTIAL = 2, /* tritt_tdp_bwd: leave the fp32 key-side partial sums in the workspace and do not
                                  write dk1/dk2/dv1/dv2 (the caller reduces them across ranks, then calls
                                  tritt_tdp_bwd_finalize) */
+  TRITT_FLAG_WIDE_OPERANDS = 4 /* triple-dot-product, bf16 inputs: form the operands with 11 significant bits (fp16
+                                 copies) instead of bf16's 8, what the reference's `convert_to_float32` asks of its TF32
+                                 dot products.  fp32 inputs always take that path on the tensor cores (head dimension
+                                 64 / 128); fp16 inputs already have it.  Needs the larger workspace that
+                                 tritt_workspace_bytes_flags() reports; an input element beyond fp16's range (65504)
+                                 sets status bit 64. */
 };
 
 /* kernel families, as reported by tritt_tdp_path() */
@@ -64,6 +71,13 @@ const char* tritt_last_error(void);
    lets the forward bound its scores and skip the row-maximum pass; a workspace without the tail is accepted and runs
    the two-pass soft-max. */
 size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype);
+/* The same for a call that will pass `flags` (TRITT_FLAG_WIDE_OPERANDS enlarges the triple-dot-product workspace of bf16
+   inputs by the fp16 operand copies; tritt_workspace_bytes() equals flags = 0). */
+size_t tritt_workspace_bytes_flags(int op, int B, int N, int T, int D, int dtype, int flags);
+
+/* Bytes of scratch tritt_tdp_fwd cannot run without for these arguments (the optional score-bound tail excluded). */
+size_t tritt_tdp_fwd_min_workspace(int B, int N, int T, int D, int dtype, int causal, int k1_window, int k2_window,
+                                   int kk_left, int kk_right, int flags);
 
 /* Which kernel family a TDP call with these arguments runs on. */
 int tritt_tdp_path(int op, int T, int D, int dtype, int causal, int k1_window, int k2_window, int kk_left,

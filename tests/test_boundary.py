@@ -64,8 +64,18 @@ def test_c_abi_rejects_bad_arguments_without_a_device():
 def test_tdp_path_selection():
     T = 512
     full = dict(causal=True, k1w=None, k2w=None, kkl=None, kkr=None)
-    # fp32 inputs always run on the general CUDA-core kernels; 16-bit ones on the tensor cores under every mask
-    assert _native.tdp_path(_native.OP_TDP_FWD, T, 64, _native.F32, **full) == _native.PATH_SIMT
+    # 16-bit inputs run on the tensor cores under every mask; fp32 inputs too when the head dimension allows (through
+    # fp16 operand copies), otherwise and with TRITT_FLAG_FORCE_SIMT on the exact-fp32 CUDA-core kernels
+    assert _native.tdp_path(_native.OP_TDP_FWD, T, 64, _native.F32, **full) == _native.PATH_TCGEN05
+    assert _native.tdp_path(_native.OP_TDP_BWD, T, 128, _native.F32, **full) == _native.PATH_TCGEN05
+    assert _native.tdp_path(_native.OP_TDP_FWD, T, 32, _native.F32, **full) == _native.PATH_SIMT
+    assert _native.tdp_path(_native.OP_TDP_FWD, T, 64, _native.F32, **full,
+                            flags=_native.FLAG_FORCE_SIMT) == _native.PATH_SIMT
+    lib = _native.lib()
+    n = 2 * 3 * T * 64
+    assert lib.tritt_workspace_bytes_flags(_native.OP_TDP_BWD, 2, 3, T, 64, _native.BF16, _native.FLAG_WIDE_OPERANDS) > \
+        lib.tritt_workspace_bytes(_native.OP_TDP_BWD, 2, 3, T, 64, _native.BF16) >= 18 * n
+    assert lib.tritt_workspace_bytes(_native.OP_TDP_FWD, 2, 3, T, 64, _native.F32) >= 14 * n
     assert _native.tdp_path(_native.OP_TDP_FWD, T, 64, _native.BF16, True, 8, 8, 4, 4) == _native.PATH_TCGEN05
     assert _native.tdp_path(_native.OP_TDP_BWD, T, 64, _native.BF16, True, 8, 8, 4, 4) == _native.PATH_TCGEN05
     assert _native.tdp_path(_native.OP_TDP_FWD, T, 64, _native.BF16, **full,
@@ -92,10 +102,18 @@ def test_python_entry_points_validate_like_the_reference():
 
 
 def test_input_precision_warns():
+    import warnings
+
+    from flash_trittention import flash_trittention
+
     q = torch.randn(1, 1, 8, 8)
     with pytest.warns(UserWarning, match="input_precision"):
         with pytest.raises(RuntimeError):
-            from flash_trittention import flash_trittention
+            flash_trittention(q, q, q, q, q, input_precision="tf32x3")
+    # "ieee" has an effect here (exact-fp32 kernels), so it does not warn
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        with pytest.raises(RuntimeError):
             flash_trittention(q, q, q, q, q, input_precision="ieee")
 
 

@@ -128,13 +128,14 @@ def test_non_contiguous_inputs_and_query_sharding():
 @pytest.mark.parametrize("D", [8, 16, 64, 128, 256])
 def test_fp32_head_dims(D):
     """Head dimensions on both CUDA-core kernel families: 16..128 run the register-resident kernels (four lanes
-    per pair row, eight at 128), the others the shared-memory kernel; windows included."""
+    per pair row, eight at 128), the others the shared-memory kernel; windows included.  ``input_precision="ieee"``
+    keeps head dimensions 64 and 128 on these exact-fp32 kernels (fp32 inputs otherwise take the tensor cores there)."""
     B, N, T, scale = 1, 2, 70, 1 / 8
     q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, scale=0.7, seed=40 + D)
     for windows in ((T, T, T, T), (20, 33, 6, 11)):
         k1w, k2w, kkl, kkr = windows
         out, grads = _run(q, k1, k2, v1, v2, dz, softmax_scale=scale, k1_window=k1w, k2_window=k2w, kk_left=kkl,
-                          kk_right=kkr, causal=True)
+                          kk_right=kkr, causal=True, input_precision="ieee")
         z_ref, _ = orc.tdp_forward(q, k1, k2, v1, v2, scale, True, k1w, k2w, kkl, kkr)
         g_ref = orc.tdp_backward(q, k1, k2, v1, v2, dz, scale, True, k1w, k2w, kkl, kkr)
         _compare(out, grads, z_ref, g_ref, (1e-4, 3e-5), (1e-3, 2e-4))
