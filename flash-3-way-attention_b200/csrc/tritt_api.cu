@@ -255,24 +255,56 @@ int tritt_dps_fwd(const void* q, const void* k1, const void* k2, const void* v1,
   return dps_fwd(a);
 }
 
-int tritt_dps_bwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, const void* o,
-                  const void* d_o, const float* m, void* dq, void* dk1, void* dk2, void* dv1, void* dv2, int B,
-                  int N, int T, int D, int dtype, float alpha, int causal, int k_diff, void* workspace,
-                  size_t workspace_bytes, int* status_word, int flags, tritt_stream_t stream) {
+static int dps_bwd_entry(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, const void* o,
+                         const void* d_o, const float* m, void* dq, void* dk1, void* dk2, void* dv1, void* dv2, int B,
+                         int N, int T, int D, int dtype, float alpha, int causal, int k_diff, void* workspace,
+                         size_t workspace_bytes, int* status_word, int flags, const void* fwd_workspace,
+                         size_t fwd_workspace_bytes, tritt_stream_t stream) {
   const void* ptrs[] = {q, k1, k2, v1, v2, o, d_o, m, dq, dk1, dk2, dv1, dv2};
   int rc = check_common(ptrs, 13, B, N, T, D, dtype);
   if (rc) return rc;
   if ((rc = check_heads(B, N))) return rc;
   if ((rc = check_windows(causal, k_diff, 0, 0, 0))) return rc;
   if ((rc = check_ws(dps_workspace(TRITT_OP_DPS_BWD, B, N, T, D, dtype), workspace, workspace_bytes))) return rc;
+  if (fwd_workspace) {
+    if ((uintptr_t)fwd_workspace & 255) {
+      set_error("the forward workspace must be 256-byte aligned");
+      return -7;
+    }
+    if (fwd_workspace_bytes < dps_workspace(TRITT_OP_DPS_FWD, B, N, T, D, dtype)) {
+      set_error("the forward workspace is smaller than tritt_workspace_bytes(TRITT_OP_DPS_FWD, ...)");
+      return -6;
+    }
+  }
   DpsArgs a{};
   a.q = q; a.k1 = k1; a.k2 = k2; a.v1 = v1; a.v2 = v2; a.o = o; a.d_o = d_o; a.m_in = m;
   a.dq = dq; a.dk1 = dk1; a.dk2 = dk2; a.dv1 = dv1; a.dv2 = dv2;
   a.B = B; a.N = N; a.T = T; a.D = D; a.dtype = dtype; a.alpha = alpha;
   a.causal = causal ? 1 : 0; a.k_diff = norm_kdiff(k_diff, T);
-  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.fwd_state = fwd_workspace;
   a.status_word = status_word; a.flags = flags; a.stream = (cudaStream_t)stream;
   return dps_bwd(a);
+}
+
+int tritt_dps_bwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, const void* o,
+                  const void* d_o, const float* m, void* dq, void* dk1, void* dk2, void* dv1, void* dv2, int B,
+                  int N, int T, int D, int dtype, float alpha, int causal, int k_diff, void* workspace,
+                  size_t workspace_bytes, int* status_word, int flags, tritt_stream_t stream) {
+  return dps_bwd_entry(q, k1, k2, v1, v2, o, d_o, m, dq, dk1, dk2, dv1, dv2, B, N, T, D, dtype, alpha, causal, k_diff,
+                       workspace, workspace_bytes, status_word, flags, nullptr, 0, stream);
+}
+
+int tritt_dps_bwd_saved(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, const void* o,
+                        const void* d_o, const float* m, void* dq, void* dk1, void* dk2, void* dv1, void* dv2, int B,
+                        int N, int T, int D, int dtype, float alpha, int causal, int k_diff, void* workspace,
+                        size_t workspace_bytes, const void* fwd_workspace, size_t fwd_workspace_bytes,
+                        int* status_word, int flags, tritt_stream_t stream) {
+  if (!fwd_workspace) {
+    set_error("tritt_dps_bwd_saved needs the forward call's workspace");
+    return -4;
+  }
+  return dps_bwd_entry(q, k1, k2, v1, v2, o, d_o, m, dq, dk1, dk2, dv1, dv2, B, N, T, D, dtype, alpha, causal, k_diff,
+                       workspace, workspace_bytes, status_word, flags, fwd_workspace, fwd_workspace_bytes, stream);
 }
 
 }  // extern "C"

@@ -112,6 +112,7 @@ struct DpsArgs {
   int causal, k_diff;
   void* workspace;
   size_t workspace_bytes;
+  const void* fwd_state;  // backward: the forward call's workspace, still holding Y, LSEin, SiLU(V1), Y*V2 (or null)
   int* status_word;
   int flags;
   cudaStream_t stream;
@@ -169,11 +170,24 @@ int sm100_silu_16(const void* in, void* out, size_t n, int dtype, cudaStream_t s
 struct AttnBwdTcArgs {
   const void *xq, *kc, *vc, *dout;  // 16-bit [BN, T, D]
   const float *bias, *lse, *drow;   // [BN, T]: per column (or null), per row, per row
+  // row owner: with `out_rows` (the attention's 16-bit output) drow[r] = dout[r] . out_rows[r] is computed by the
+  // kernel, used, and stored to `drow_out` for the column-owner launch that follows
+  const void* out_rows;
+  float* drow_out;
   void* d_rows_t;
   const float* d_rows_add;          // [BN, T, D] or null
   float* d_kc_f32;
   void* d_kc_t;
-  float* d_vc_f32;
+  float* d_vc_f32;                  // column owner: sum_r P dout, fp32, or null when one of the two forms below is asked
+  // column owner, instead of d_vc_f32: d_vc_t = d_vc * SiLU'(silu_src)  (16-bit; silu_src = the raw value tensor)
+  const void* silu_src;
+  void* d_vc_t;
+  // column owner, instead of d_vc_f32 (with dW = d_vc): mid_dv2 = dW * mid_y, mid_dy_t = dW * mid_v2 (both 16-bit),
+  // mid_dt[c] = sum_h (dW mid_v2 mid_y)[c, h] - gsum[c]
+  const float* mid_y;
+  const void* mid_v2;
+  void *mid_dv2, *mid_dy_t;
+  float* mid_dt;
   float* gsum;                      // [BN, T] or null
   int BN, T, D, dtype, causal, win;
   float alpha;

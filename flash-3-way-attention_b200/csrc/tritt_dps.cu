@@ -15,39 +15,41 @@
 namespace tritt {
 namespace {
 
-// workspace layout (floats): Y [n] | LSEin [r] | then, backward only:
-//   Dq [r] | dW [n] | g [r] | dY [n] | Dt [r] | dK2a [n] | dsV1 [n]
-// Every segment starts on a 256-byte boundary (lengths are rounded up to 64 floats): the tensor-core kernels
-// store the [n] buffers with 16-byte vector stores, and r = B*N*T may be odd.
+// workspace layout: the forward's state  Y [n] fp32 | LSEin [r] fp32 | SiLU(V1) [n] | Y*V2 [n]  (the last two in the
+// inputs' 16-bit type, absent for fp32 inputs), then, backward only, fp32
+//   Dq [r] | dW [n] | g [r] | dY [n] | Dt [r] | dK2a [n] | dsV1 [n]   and   dY [n] in the 16-bit type.
+// A backward that is handed the forward's workspace (`fwd_state`) reads the state there instead of recomputing it.
+// Every segment starts on a 256-byte boundary (lengths are rounded up): the tensor-core kernels store the [n]
+// buffers with 16-byte vector stores, and r = B*N*T may be odd.
 struct DpsWs {
   float *Y, *lse_in, *Dq, *dW, *g, *dY, *Dt, *dK2a, *dsV1;
   void *sv1_16, *w_16, *dy_16;  // tensor-core path only: SiLU(V1), Y*V2 and dY in the inputs' 16-bit type
 };
-size_t dps_float_bytes(int op, size_t n, size_t r) {
-  n = align_up(n, 64);
-  r = align_up(r, 64);
-  return (op == TRITT_OP_DPS_FWD ? n + r : 5 * n + 4 * r) * sizeof(float);
+size_t dps_state_bytes(size_t n, size_t r, int dtype) {
+  return (align_up(n, 64) + align_up(r, 64)) * sizeof(float) + (dtype == TRITT_F32 ? 0 : 2 * align_up(n * 2, 256));
 }
 // The tensor-core forward serves 16-bit inputs with head dimension 64 or 128 and a non-negative k_diff.
 bool dps_fwd_on_tensor_cores(const DpsArgs& a) {
   return !(a.flags & TRITT_FLAG_FORCE_SIMT) && a.k_diff >= 0 && sm100_attn_fwd_supported(a.T, a.D, a.dtype);
 }
-DpsWs carve(void* ws, size_t n, size_t r, int op) {
-  float* f = (float*)ws;
-  const size_t np = align_up(n, 64), rp = align_up(r, 64);
+DpsWs carve(void* ws, const void* fwd_state, size_t n, size_t r, int dtype) {
+  const size_t np = align_up(n, 64), rp = align_up(r, 64), h = align_up(n * 2, 256);
   DpsWs w;
-  w.Y = f; f += np;
-  w.lse_in = f; f += rp;
+  // the state: in the forward's own workspace when the caller kept it, else at the head of this one
+  char* st = fwd_state ? (char*)const_cast<void*>(fwd_state) : (char*)ws;
+  w.Y = (float*)st;
+  w.lse_in = w.Y + np;
+  w.sv1_16 = st + (np + rp) * sizeof(float);
+  w.w_16 = (char*)w.sv1_16 + h;
+  float* f = (float*)((char*)ws + dps_state_bytes(n, r, dtype));
   w.Dq = f; f += rp;
   w.dW = f; f += np;
   w.g = f; f += rp;
   w.dY = f; f += np;
   w.Dt = f; f += rp;
   w.dK2a = f; f += np;
-  w.dsV1 = f;
-  w.sv1_16 = (char*)ws + dps_float_bytes(op, n, r);
-  w.w_16 = (char*)w.sv1_16 + align_up(n * 2, 256);
-  w.dy_16 = (char*)w.w_16 + align_up(n * 2, 256);  // (backward only)
+  w.dsV1 = f; f += np;
+  w.dy_16 = f;  // (16-bit inputs only)
   return w;
 }
 
@@ -88,7 +90,7 @@ int dps_inner_fwd(const DpsArgs& a, const DpsWs& w) {
 template <typename T>
 int dps_fwd_t(const DpsArgs& a) {
   const size_t n = (size_t)a.B * a.N * a.T * a.D, r = (size_t)a.B * a.N * a.T;
-  DpsWs w = carve(a.workspace, n, r, TRITT_OP_DPS_FWD);
+  DpsWs w = carve(a.workspace, nullptr, n, r, a.dtype);
   if (dps_fwd_on_tensor_cores(a)) return dps_fwd_tensor_cores(a, w, false);
   int rc = dps_inner_fwd<T>(a, w);
   if (rc) return rc;
@@ -106,13 +108,12 @@ int dps_fwd_t(const DpsArgs& a) {
 // Backward with every attention product on the tensor cores (same eligibility as the forward).
 template <typename T>
 int dps_bwd_tensor_cores(const DpsArgs& a, const DpsWs& w) {
-  const size_t n = (size_t)a.B * a.N * a.T * a.D, r = (size_t)a.B * a.N * a.T;
-  int rc = dps_fwd_tensor_cores(a, w, true);  // Y, LSEin, Y*V2 again: cheaper than saving them
-  if (rc) return rc;
-  rowdot_kernel<T><<<(unsigned)((r + 3) / 4), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
-  count_launch();
-  TRITT_CUDA_OK(cudaGetLastError());
-  // ---- outer attention: rows q (Q), columns t (K2, W = Y*V2, bias LSEin)
+  int rc = 0;
+  // Y, LSEin, SiLU(V1), Y*V2: taken from the forward's workspace when the caller kept it, else computed again
+  if (!a.fwd_state && (rc = dps_fwd_tensor_cores(a, w, true))) return rc;
+  // ---- outer attention: rows q (Q), columns t (K2, W = Y*V2, bias LSEin).  The row owner also forms
+  // Dq = sum_h dO O per query and leaves it for the column owner; the column owner's epilogue turns dW into
+  // dV2 = dW * Y, dY = dW * V2 and the inner attention's row term Dt = sum_h dY Y - sum_q dS.
   AttnBwdTcArgs o{};
   o.xq = a.q; o.kc = a.k2; o.vc = w.w_16; o.dout = a.d_o;
   o.bias = w.lse_in; o.lse = a.m_in; o.drow = w.Dq;
@@ -120,14 +121,12 @@ int dps_bwd_tensor_cores(const DpsArgs& a, const DpsWs& w) {
   o.alpha = a.alpha; o.status = a.status_word; o.stream = a.stream;
   AttnBwdTcArgs orow = o;
   orow.d_rows_t = a.dq;
+  orow.out_rows = a.o; orow.drow_out = w.Dq;
   if ((rc = sm100_attn_bwd_rows(orow))) return rc;
   AttnBwdTcArgs ocol = o;
-  ocol.d_kc_f32 = w.dK2a; ocol.d_vc_f32 = w.dW; ocol.gsum = w.g;
+  ocol.d_kc_f32 = w.dK2a;
+  ocol.mid_y = w.Y; ocol.mid_v2 = a.v2; ocol.mid_dv2 = a.dv2; ocol.mid_dy_t = w.dy_16; ocol.mid_dt = w.Dt;
   if ((rc = sm100_attn_bwd_cols(ocol))) return rc;
-  dps_mid_kernel<T><<<(unsigned)((r + 3) / 4), 128, 0, a.stream>>>(w.dW, w.Y, (const T*)a.v2, w.g, (T*)a.dv2, w.dY,
-                                                                        w.Dt, r, a.D, (T*)w.dy_16);
-  count_launch();
-  TRITT_CUDA_OK(cudaGetLastError());
   // ---- inner attention: rows t (K2), columns s (K1, SiLU(V1)); upstream gradient dY
   AttnBwdTcArgs i{};
   i.xq = a.k2; i.kc = a.k1; i.vc = w.sv1_16; i.dout = w.dy_16;
@@ -139,22 +138,19 @@ int dps_bwd_tensor_cores(const DpsArgs& a, const DpsWs& w) {
   irow.d_rows_add = w.dK2a;
   if ((rc = sm100_attn_bwd_rows(irow))) return rc;
   AttnBwdTcArgs icol = i;
-  icol.d_kc_t = a.dk1; icol.d_vc_f32 = w.dsV1;
-  if ((rc = sm100_attn_bwd_cols(icol))) return rc;
-  dps_dv1_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, a.stream>>>(w.dsV1, (const T*)a.v1, (T*)a.dv1, n);
-  count_launch();
-  TRITT_CUDA_OK(cudaGetLastError());
-  return 0;
+  icol.d_kc_t = a.dk1;
+  icol.silu_src = a.v1; icol.d_vc_t = a.dv1;  // dV1 = dSiLU(V1) * SiLU'(V1) in the epilogue
+  return sm100_attn_bwd_cols(icol);
 }
 
 template <typename T>
 int dps_bwd_t(const DpsArgs& a) {
   const size_t n = (size_t)a.B * a.N * a.T * a.D, r = (size_t)a.B * a.N * a.T;
-  DpsWs w = carve(a.workspace, n, r, TRITT_OP_DPS_BWD);
+  DpsWs w = carve(a.workspace, a.fwd_state, n, r, a.dtype);
   if (dps_fwd_on_tensor_cores(a)) return dps_bwd_tensor_cores<T>(a, w);
   const int BN = a.B * a.N;
-  // inner leg again (Y, LSEin): cheaper than saving it between forward and backward
-  int rc = dps_inner_fwd<T>(a, w);
+  // inner leg again (Y, LSEin) unless the caller kept the forward's workspace
+  int rc = a.fwd_state ? 0 : dps_inner_fwd<T>(a, w);
   if (rc) return rc;
   rowdot_kernel<T><<<(unsigned)((r + 3) / 4), 128, 0, a.stream>>>((const T*)a.d_o, (const T*)a.o, w.Dq, r, a.D);
   count_launch();
@@ -213,9 +209,10 @@ int dps_bwd_t(const DpsArgs& a) {
 
 size_t dps_workspace(int op, int B, int N, int T, int D, int dtype) {
   const size_t n = (size_t)B * N * T * D, r = (size_t)B * N * T;
-  // SiLU(V1), Y*V2 and (backward) dY in the inputs' type
-  const size_t scratch16 = dtype == TRITT_F32 ? 0 : (op == TRITT_OP_DPS_FWD ? 2 : 3) * align_up(n * 2, 256);
-  return dps_float_bytes(op, n, r) + scratch16;
+  const size_t np = align_up(n, 64), rp = align_up(r, 64);
+  const size_t state = dps_state_bytes(n, r, dtype);
+  if (op == TRITT_OP_DPS_FWD) return state;
+  return state + (4 * np + 3 * rp) * sizeof(float) + (dtype == TRITT_F32 ? 0 : align_up(n * 2, 256));
 }
 
 int dps_fwd(const DpsArgs& a) {

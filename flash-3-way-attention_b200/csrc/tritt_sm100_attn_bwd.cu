@@ -39,6 +39,14 @@ template <int D> struct AttnBwdCfg {
 
 struct AttnBwdParams {
   const float *bias, *lse, *drow;  // per column (or null); per row; per row
+  const void *out_rows, *dout_rows;  // row-owner: drow = dout . out computed here (then drow is not read) ...
+  float* drow_out;                   // ... and stored for the column-owner launch
+  const void* silu_src;            // column-owner epilogue variants (see AttnBwdTcArgs)
+  void* d_vc_t;
+  const float* mid_y;
+  const void* mid_v2;
+  void *mid_dv2, *mid_dy_t;
+  float* mid_dt;
   void* d_rows_t;                  // row-owner: 16-bit [BN, T, D]
   const float* d_rows_add;         // row-owner: fp32 term added before rounding, or null
   float* d_kc_f32;                 // column-owner: one of the two
@@ -236,7 +244,26 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmOwn0, const __grid_c
         own_a = p.bias ? __ldg(p.bias + (size_t)bh * T + own) * kLog2e : 0.f;
       } else {
         own_a = __ldg(p.lse + (size_t)bh * T + own) * kLog2e;
-        own_b = __ldg(p.drow + (size_t)bh * T + own);
+        if (p.out_rows) {
+          // drow = sum_h dOut[own, h] Out[own, h]  (the reference's preprocess kernel, bwd_preprocess.py:5-49)
+          const uint4* a4 = reinterpret_cast<const uint4*>((const T16*)p.dout_rows + ((size_t)bh * T + own) * D);
+          const uint4* b4 = reinterpret_cast<const uint4*>((const T16*)p.out_rows + ((size_t)bh * T + own) * D);
+          float acc = 0.f;
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i) {
+            const uint4 av = __ldg(a4 + i), bv = __ldg(b4 + i);
+            const uint32_t aw[4] = {av.x, av.y, av.z, av.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 fa = unpack2<T16>(aw[e]), fb = unpack2<T16>(bw[e]);
+              acc = fmaf(fa.x, fb.x, fmaf(fa.y, fb.y, acc));
+            }
+          }
+          own_b = acc;
+          p.drow_out[(size_t)bh * T + own] = acc;
+        } else {
+          own_b = __ldg(p.drow + (size_t)bh * T + own);
+        }
       }
     }
     // attended indices of the other side for this owner: [j_lo, j_hi]
@@ -316,6 +343,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmOwn0, const __grid_c
     if (alive) {
       tc_fence_after();
       const size_t off = ((size_t)bh * T + own) * D;
+      float mid_dot = 0.f;  // column owner with the `mid` epilogue: sum_h dY Y of this column
 #pragma unroll
       for (int ch = 0; ch < D / 32; ++ch) {
         uint32_t a0[32];
@@ -326,11 +354,51 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmOwn0, const __grid_c
           tmem_ld32(tmem + lane_base + Cfg::kTmemAcc1 + ch * 32, a1);
           tmem_wait_ld();
           if (!own_ok) continue;
+          if (p.d_vc_f32) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            *reinterpret_cast<float4*>(p.d_vc_f32 + off + ch * 32 + e) =
-                make_float4(__uint_as_float(a0[e]), __uint_as_float(a0[e + 1]), __uint_as_float(a0[e + 2]),
-                            __uint_as_float(a0[e + 3]));
+            for (int e = 0; e < 32; e += 4)
+              *reinterpret_cast<float4*>(p.d_vc_f32 + off + ch * 32 + e) =
+                  make_float4(__uint_as_float(a0[e]), __uint_as_float(a0[e + 1]), __uint_as_float(a0[e + 2]),
+                              __uint_as_float(a0[e + 3]));
+          } else if (p.silu_src) {
+            // d(value) of a SiLU-gated value tensor: times SiLU'(raw value), in the operands' type
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              const uint4 rv = __ldg(reinterpret_cast<const uint4*>((const T16*)p.silu_src + off + ch * 32 + e));
+              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+              uint32_t o4[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float2 f = unpack2<T16>(rw[k]);
+                o4[k] = pack2<T16>(__uint_as_float(a0[e + 2 * k]) * silu_grad_f(f.x),
+                                   __uint_as_float(a0[e + 2 * k + 1]) * silu_grad_f(f.y));
+              }
+              *reinterpret_cast<uint4*>((T16*)p.d_vc_t + off + ch * 32 + e) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+          } else {
+            // value tensor W = Y * V2 of the outer attention: dV2 = dW * Y, dY = dW * V2, and the row term of the
+            // inner attention's backward, sum_h dY Y (minus the column sums of dS, below)
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              const uint4 vv = __ldg(reinterpret_cast<const uint4*>((const T16*)p.mid_v2 + off + ch * 32 + e));
+              const float4 y0 = __ldg(reinterpret_cast<const float4*>(p.mid_y + off + ch * 32 + e));
+              const float4 y1 = __ldg(reinterpret_cast<const float4*>(p.mid_y + off + ch * 32 + e + 4));
+              const float yy[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+              const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
+              uint32_t o_dv2[4], o_dy[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float2 f = unpack2<T16>(vw[k]);
+                const float w0 = __uint_as_float(a0[e + 2 * k]), w1 = __uint_as_float(a0[e + 2 * k + 1]);
+                const float dy0 = w0 * f.x, dy1 = w1 * f.y;
+                mid_dot = fmaf(dy0, yy[2 * k], fmaf(dy1, yy[2 * k + 1], mid_dot));
+                o_dv2[k] = pack2<T16>(w0 * yy[2 * k], w1 * yy[2 * k + 1]);
+                o_dy[k] = pack2<T16>(dy0, dy1);
+              }
+              *reinterpret_cast<uint4*>((T16*)p.mid_dv2 + off + ch * 32 + e) = make_uint4(o_dv2[0], o_dv2[1], o_dv2[2], o_dv2[3]);
+              *reinterpret_cast<uint4*>((T16*)p.mid_dy_t + off + ch * 32 + e) = make_uint4(o_dy[0], o_dy[1], o_dy[2], o_dy[3]);
+            }
+          }
           float v[32];
 #pragma unroll
           for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(a1[e]) * p.alpha;
@@ -368,6 +436,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmOwn0, const __grid_c
         }
       }
       if (COL && own_ok && p.gsum) p.gsum[(size_t)bh * T + own] = gs;
+      if (COL && own_ok && p.mid_dt) p.mid_dt[(size_t)bh * T + own] = mid_dot - gs;
     }
   }
 
@@ -389,6 +458,9 @@ int launch_attn_bwd(const AttnBwdTcArgs& a) {
   if ((rc = make_tmap_3d(&tmDO, a.dout, 2, D, a.T, a.BN, 64, 128))) return rc;
   AttnBwdParams p{};
   p.bias = a.bias; p.lse = a.lse; p.drow = a.drow;
+  p.out_rows = a.out_rows; p.dout_rows = a.dout; p.drow_out = a.drow_out;
+  p.silu_src = a.silu_src; p.d_vc_t = a.d_vc_t;
+  p.mid_y = a.mid_y; p.mid_v2 = a.mid_v2; p.mid_dv2 = a.mid_dv2; p.mid_dy_t = a.mid_dy_t; p.mid_dt = a.mid_dt;
   p.d_rows_t = a.d_rows_t; p.d_rows_add = a.d_rows_add;
   p.d_kc_f32 = a.d_kc_f32; p.d_kc_t = a.d_kc_t; p.d_vc_f32 = a.d_vc_f32; p.gsum = a.gsum;
   p.T = a.T; p.causal = a.causal; p.win = a.win < 0 ? 0 : (a.win > a.T ? a.T : a.win);

@@ -26,13 +26,14 @@ SYMBOLS = (
     "tritt_version", "tritt_kernel_launches", "tritt_last_error", "tritt_workspace_bytes", "tritt_workspace_bytes_flags",
     "tritt_tdp_fwd_min_workspace", "tritt_tdp_path", "tritt_dps_path", "tritt_tdp_fwd",
     "tritt_tdp_bwd", "tritt_tdp_bwd_finalize", "tritt_tdp_bwd_partials_offset", "tritt_dps_fwd",
-    "tritt_dps_bwd", "tritt_selftest_umma", "tritt_selftest_wait_expiry", "tritt_tdp_fwd_noalloc",
+    "tritt_dps_bwd", "tritt_dps_bwd_saved", "tritt_selftest_umma", "tritt_selftest_wait_expiry", "tritt_tdp_fwd_noalloc",
     "tritt_noalloc_scratch_bytes",
 )
 
 _lib = None
 _lock = threading.Lock()
 _status = {}  # device index -> pinned int32 status word (created under _lock)
+_status_np = {}  # device index -> numpy view of the same word (a host read without any tensor machinery)
 launches = 0  # kernels-enqueuing library calls made by this process (bench bookkeeping)
 
 
@@ -77,6 +78,8 @@ def lib():
                 L.tritt_dps_fwd.argtypes = [vp] * 7 + [i] * 5 + [f] + [i] * 2 + [vp, sz, vp, i, vp]
                 L.tritt_dps_bwd.restype = i
                 L.tritt_dps_bwd.argtypes = [vp] * 13 + [i] * 5 + [f] + [i] * 2 + [vp, sz, vp, i, vp]
+                L.tritt_dps_bwd_saved.restype = i
+                L.tritt_dps_bwd_saved.argtypes = [vp] * 13 + [i] * 5 + [f] + [i] * 2 + [vp, sz, vp, sz, vp, i, vp]
                 L.tritt_tdp_fwd_noalloc.restype = i
                 L.tritt_tdp_fwd_noalloc.argtypes = [vp] * 7 + [i] * 5 + [f] + [i] * 5 + [vp, i, vp]
                 L.tritt_noalloc_scratch_bytes.restype = sz
@@ -127,6 +130,7 @@ def status_word(device) -> torch.Tensor:
             t = _status.get(key)
             if t is None:
                 t = torch.zeros(1, dtype=torch.int32).pin_memory()
+                _status_np[key] = t.numpy()
                 _status[key] = t
     return t
 
@@ -150,6 +154,12 @@ def check_status(device=None, synchronize: bool = True) -> None:
     then invalid).  With ``synchronize=False`` only kernels that have already finished are seen; every compute
     entry point of this module makes that cheap check on entry, so a time-out surfaces at the latest on the next
     call after the failed kernel has retired."""
+    if not synchronize:
+        # the per-call check: one host read of the pinned word
+        idx = device.index if isinstance(device, torch.device) else None
+        arr = _status_np.get(idx) if idx is not None else None
+        if arr is not None and arr[0] == 0:
+            return
     dev = _device_index(torch.cuda.current_device() if device is None else device)
     if synchronize:
         v = read_status(dev)
@@ -180,6 +190,25 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+class _on_device:
+    """``torch.cuda.device(dev)`` only when ``dev`` is not already the current device (the common case costs one
+    query instead of a get / set / restore)."""
+
+    __slots__ = ("ctx",)
+
+    def __init__(self, dev: torch.device):
+        self.ctx = None if dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            return self.ctx.__exit__(*exc)
+        return False
+
+
 def _win(w, T):
     return T if w is None else int(w)
 
@@ -199,7 +228,7 @@ def tdp_fwd(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr, q_mod=
     B, N, T, D = q.shape
     dt = dtype_code(q.dtype)
     check_status(q.device, synchronize=False)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         if ws is None:
             ws = workspace(OP_TDP_FWD, B, N, T, D, dt, q.device, flags)
         rc = lib().tritt_tdp_fwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
@@ -218,7 +247,7 @@ def tdp_bwd(q, k1, k2, v1, v2, o, do, lse, dq, dk1, dk2, dv1, dv2, alpha, causal
     dt = dtype_code(q.dtype)
     ptr = lambda t: 0 if t is None else t.data_ptr()
     check_status(q.device, synchronize=False)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         if ws is None:
             ws = workspace(OP_TDP_BWD, B, N, T, D, dt, q.device, flags)
         rc = lib().tritt_tdp_bwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
@@ -235,7 +264,7 @@ def tdp_bwd_finalize(v1, dk1, dk2, dv1, dv2, ws):
     global launches
     B, N, T, D = v1.shape
     check_status(v1.device, synchronize=False)
-    with torch.cuda.device(v1.device):
+    with _on_device(v1.device):
         rc = lib().tritt_tdp_bwd_finalize(v1.data_ptr(), dk1.data_ptr(), dk2.data_ptr(), dv1.data_ptr(),
                                           dv2.data_ptr(), B, N, T, D, dtype_code(v1.dtype), ws.data_ptr(),
                                           ws.numel(), _stream())
@@ -244,11 +273,13 @@ def tdp_bwd_finalize(v1, dk1, dk2, dv1, dv2, ws):
 
 
 def dps_fwd(q, k1, k2, v1, v2, o, m, alpha, causal, k_diff, flags=0):
+    """Returns the workspace tensor: handed to ``dps_bwd(..., fwd_ws=...)`` it spares the backward the inner
+    attention's recomputation (keep it untouched until then)."""
     global launches
     B, N, T, D = q.shape
     dt = dtype_code(q.dtype)
     check_status(q.device, synchronize=False)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         ws = workspace(OP_DPS_FWD, B, N, T, D, dt, q.device)
         rc = lib().tritt_dps_fwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
                                  o.data_ptr(), m.data_ptr(), B, N, T, D, dt, float(alpha), int(bool(causal)),
@@ -256,20 +287,25 @@ def dps_fwd(q, k1, k2, v1, v2, o, m, alpha, causal, k_diff, flags=0):
                                  _stream())
     _check(rc, "tritt_dps_fwd")
     launches += 1
+    return ws
 
 
-def dps_bwd(q, k1, k2, v1, v2, o, do, m, dq, dk1, dk2, dv1, dv2, alpha, causal, k_diff, flags=0):
+def dps_bwd(q, k1, k2, v1, v2, o, do, m, dq, dk1, dk2, dv1, dv2, alpha, causal, k_diff, flags=0, fwd_ws=None):
+    """``fwd_ws``: the tensor ``dps_fwd`` returned for the same inputs, if it was kept untouched."""
     global launches
     B, N, T, D = q.shape
     dt = dtype_code(q.dtype)
     check_status(q.device, synchronize=False)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         ws = workspace(OP_DPS_BWD, B, N, T, D, dt, q.device)
-        rc = lib().tritt_dps_bwd(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
-                                 o.data_ptr(), do.data_ptr(), m.data_ptr(), dq.data_ptr(), dk1.data_ptr(),
-                                 dk2.data_ptr(), dv1.data_ptr(), dv2.data_ptr(), B, N, T, D, dt, float(alpha),
-                                 int(bool(causal)), int(k_diff), ws.data_ptr(), ws.numel(),
-                                 status_word(q.device).data_ptr(), flags, _stream())
+        args = (q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(), o.data_ptr(), do.data_ptr(),
+                m.data_ptr(), dq.data_ptr(), dk1.data_ptr(), dk2.data_ptr(), dv1.data_ptr(), dv2.data_ptr(), B, N, T, D,
+                dt, float(alpha), int(bool(causal)), int(k_diff), ws.data_ptr(), ws.numel())
+        if fwd_ws is None:
+            rc = lib().tritt_dps_bwd(*args, status_word(q.device).data_ptr(), flags, _stream())
+        else:
+            rc = lib().tritt_dps_bwd_saved(*args, fwd_ws.data_ptr(), fwd_ws.numel(), status_word(q.device).data_ptr(),
+                                           flags, _stream())
     _check(rc, "tritt_dps_bwd")
     launches += 1
 
@@ -281,7 +317,7 @@ def tdp_fwd_noalloc(q, k1, k2, v1, v2, o, lse, alpha, causal, k1w, k2w, kkl, kkr
     global launches
     B, N, T, D = q.shape
     check_status(q.device, synchronize=False)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         rc = lib().tritt_tdp_fwd_noalloc(q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(),
                                          o.data_ptr(), lse.data_ptr(), B, N, T, D, dtype_code(q.dtype), float(alpha),
                                          int(bool(causal)), _win(k1w, T), _win(k2w, T), _win(kkl, T), _win(kkr, T),

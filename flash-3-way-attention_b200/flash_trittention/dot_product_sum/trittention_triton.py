@@ -39,7 +39,10 @@ class TrittentionTritonFunction(torch.autograd.Function):
         # convert_to_float32 asks for fp32 operands inside the kernels (reference trittention_triton.py:98-117
         # forwards it to its launches): the CUDA-core path computes in fp32 on every dtype
         flags = _native.FLAG_FORCE_SIMT if (convert_to_float32 or input_precision == "ieee") else 0
-        _native.dps_fwd(q, k1, k2, v1, v2, o, m, softmax_scale, causal, k_diff, flags=flags)
+        ws = _native.dps_fwd(q, k1, k2, v1, v2, o, m, softmax_scale, causal, k_diff, flags=flags)
+        # the forward's workspace holds the inner attention's results; kept for the backward (the reference saves
+        # only the inputs, o and m and recomputes, trittention_triton.py:122-128)
+        ctx.fwd_ws = ws if any(ctx.needs_input_grad[:5]) else None
         ctx.flags = flags
         ctx.causal = causal
         ctx.softmax_scale = softmax_scale
@@ -57,7 +60,8 @@ class TrittentionTritonFunction(torch.autograd.Function):
         grad_output = _native.aligned(grad_output)
         dq, dk1, dk2, dv1, dv2 = (torch.empty_like(q) for _ in range(5))
         _native.dps_bwd(q, k1, k2, v1, v2, o, grad_output, m, dq, dk1, dk2, dv1, dv2, ctx.softmax_scale,
-                        ctx.causal, ctx.k_diff, flags=ctx.flags)
+                        ctx.causal, ctx.k_diff, flags=ctx.flags, fwd_ws=ctx.fwd_ws)
+        ctx.fwd_ws = None
         return dq, dk1, dk2, dv1, dv2, None, None, None, None, None
 
 

@@ -145,6 +145,19 @@ int tritt_dps_bwd(const void* q, const void* k1, const void* k2, const void* v1,
                   size_t workspace_bytes, int* status_word, int flags, tritt_stream_t stream);
 
 /*
+ * The same backward for a caller that kept the forward call's workspace untouched (same inputs, same arguments):
+ * the inner attention's results the forward left there (Y, its log-sum-exp, SiLU(V1), Y*V2) are read instead of being
+ * computed again, which removes two launches.  `workspace` is still this call's own scratch of
+ * tritt_workspace_bytes(TRITT_OP_DPS_BWD, ...) bytes.  The reference keeps no such state between its forward and
+ * backward (it recomputes per query block, dot_product_sum/kernels/bwd_dq_kernel.py:28-350).
+ */
+int tritt_dps_bwd_saved(const void* q, const void* k1, const void* k2, const void* v1, const void* v2, const void* o,
+                        const void* d_o, const float* m, void* dq, void* dk1, void* dk2, void* dv1, void* dv2, int B,
+                        int N, int T, int D, int dtype, float alpha, int causal, int k_diff, void* workspace,
+                        size_t workspace_bytes, const void* fwd_workspace, size_t fwd_workspace_bytes,
+                        int* status_word, int flags, tritt_stream_t stream);
+
+/*
  * Triple-dot-product forward for callers that may not allocate device memory (a plugin inside
  * another program's enqueue hook, a process whose device memory all belongs to a pool this call
  * site cannot use, a section that must avoid the allocator's device-wide synchronisation).

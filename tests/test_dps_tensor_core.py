@@ -125,3 +125,24 @@ def test_odd_number_of_rows(N, T, D):
     g_ref = orc.dps_backward(*[x.float() for x in (q, k1, k2, v1, v2, dz)], scale, True, T)
     for name, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), grads, g_ref):
         assert_close(name, a.cpu(), b, dtype)
+
+
+@pytest.mark.parametrize("dtype,T,D,k_diff", [(torch.float16, 300, 64, 130), (torch.bfloat16, 129, 128, 129),
+                                              (torch.float32, 70, 32, 9)])
+def test_backward_with_the_forward_workspace_equals_the_recomputing_backward(dtype, T, D, k_diff):
+    """``tritt_dps_bwd_saved`` reads the inner attention's results from the forward call's workspace instead of
+    computing them again: same kernels on the same data, so the gradients are identical."""
+    B, N, scale = 1, 2, 1 / 8
+    q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, seed=T + 3, dtype=dtype)
+    t = [x.to(DEV) for x in (q, k1, k2, v1, v2)]
+    dzd = dz.to(DEV)
+    o = torch.empty_like(t[0])
+    m = torch.empty(B, N, T, dtype=torch.float32, device=DEV)
+    fwd_ws = _native.dps_fwd(*t, o, m, scale, True, k_diff)
+    a = [torch.empty_like(t[0]) for _ in range(5)]
+    _native.dps_bwd(*t, o, dzd, m, *a, scale, True, k_diff, fwd_ws=fwd_ws)
+    b = _bwd(t, o, m, dzd, scale, True, k_diff)
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0
+    for name, x, y in zip(("dq", "dk1", "dk2", "dv1", "dv2"), a, b):
+        assert torch.equal(x, y), name
