@@ -13,10 +13,13 @@
 // (b200/README.md:61-67) and benchmarks the case (b200/bench_b200.py:113: windows 128/128/32/32 at T = 2048).
 //
 // CTA layout (persistent, 512 threads), two tiles in flight (tile t uses slot t & 1 of every per-tile resource):
-//   warp 0       TMA producer: the 32-row K2 block of a tile, then its K1 and SiLU(V1) slabs into a 4-stage ring
+//   warp 0       TMA producer: the 32-row K2 and V2 blocks of a tile (four tiles ahead at head dimension 64), then its K1
+//                and SiLU(V1) slabs into a ring of eight stages (four at head dimension 128)
 //   warp 1       tcgen05.mma issuer: S(t), then P V of tile t - 1, so that a tile's soft-max overlaps its neighbour's products
 //   warps 4-7    soft-max warpgroup of slot 0, warps 8-11 of slot 1 (one row per thread; they also form A)
-//   warps 12-15  fold warpgroup: warp g owns query q_g
+//   warps 12-15  fold warpgroup: warp g owns query q_g (the V2 factor comes from the block in shared memory)
+// The kernel is bound by the instruction issue of the soft-max and fold warps (a tile is 16 K exponentials with
+// per-element column masks for ~12 M flop), not by the tensor pipe or by memory.
 #include "tritt_common.cuh"
 #include "tritt_sm100.cuh"
 #include "tritt_sm100_tdp.cuh"
@@ -33,21 +36,25 @@ constexpr int kRK = 32;   // K2 rows per tile
 
 template <int D> struct BandCfg {
   static constexpr int kTileA = 128 * D * 2;          // one 128-row operand / K1 / SiLU(V1) tile
-  static constexpr int kStages = 4;
-  static constexpr int kRawBytes = kRK * D * 2;       // the K2 block as loaded
+  // K1 / SiLU(V1) slabs in flight: a tile is a short chain of dependent steps (fetch, operand, scores, soft-max,
+  // values), so the fetches have to run several tiles ahead; head dimension 128 leaves room for four stages only
+  static constexpr int kStages = D == 64 ? 8 : 4;
+  static constexpr int kRawSlots = D == 64 ? 4 : 2;   // (K2, V2) blocks in flight
+  static constexpr int kBlockBytes = kRK * D * 2;     // one 32-row block as loaded
+  static constexpr int kRawBytes = 2 * kBlockBytes;   // the K2 block, then the V2 block of the same rows
   static constexpr int kOffA = 0;                     // A of slot 0, slot 1
   static constexpr int kOffRing = 2 * kTileA;
-  static constexpr int kOffRaw = kOffRing + kStages * kTileA;   // 2 slots (each a multiple of 4 KiB: 1024-aligned)
-  static constexpr int kOffStats = kOffRaw + 2 * kRawBytes;     // [2 slots][128][2] fp32: row (reference, sum)
+  static constexpr int kOffRaw = kOffRing + kStages * kTileA;   // (each slot a multiple of 4 KiB: 1024-aligned)
+  static constexpr int kOffStats = kOffRaw + kRawSlots * kRawBytes;  // [2 slots][128][2] fp32: row (reference, sum)
   static constexpr int kOffBars = kOffStats + 2 * 128 * 2 * 4;
-  static constexpr int kSmem = kOffBars + 256;
+  static constexpr int kSmem = kOffBars + 384;
   static constexpr int kTmemAcc = 256;                // S_0 | S_1 | acc_0 | acc_1
 };
 
 struct BandParams {
   void* out;
   float* lse;
-  const void *q, *v2;
+  const void* q;
   int T, BN, nq, q_mod, q_rem, n_groups;
   int k1w, k2w, kkl, kkr;
   float scale2;               // alpha * log2(e)
@@ -57,27 +64,28 @@ struct BandParams {
 };
 
 struct BandBarriers {
-  uint64_t ring_full[4], ring_empty[4];
-  uint64_t k2_full[2], a_ready[2], a_free[2], s_ready[2], p_ready[2], o_done[2], o_free[2], stats_ready[2];
+  uint64_t ring_full[8], ring_empty[8];
+  uint64_t k2_full[4], raw_free[4];  // per (K2, V2) block slot (tile t uses slot t % kRawSlots)
+  uint64_t a_ready[2], s_ready[2], p_ready[2], o_done[2], o_free[2], stats_ready[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
 // One tile of the walk: queries q_0 .. q_last of a group, the K2 block starting at kb0, the K1 slab starting at jlo.
 struct BandTile {
-  int bh, q0, count, kb0, jlo, nks;
+  int bh, q0, count, kb0, jlo;
   bool first, last;  // first / last k-block of its query group
 };
 
 template <int D, typename T16>
 __global__ void __launch_bounds__(kBandThreads, 1)
 tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__ CUtensorMap tmK2b,
-                    const __grid_constant__ CUtensorMap tmSV1, BandParams p) {
+                    const __grid_constant__ CUtensorMap tmV2b, const __grid_constant__ CUtensorMap tmSV1, BandParams p) {
   using Cfg = BandCfg<D>;
   constexpr int NS = Cfg::kStages;
   constexpr int KH = D / 64;
   extern __shared__ __align__(1024) uint8_t smem[];
-  static_assert(sizeof(BandBarriers) <= 256, "barrier block too large");
+  static_assert(sizeof(BandBarriers) <= 384, "barrier block too large");
   BandBarriers& bars = *reinterpret_cast<BandBarriers*>(smem + Cfg::kOffBars);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (smem_u32(smem) & 1023u) {
@@ -90,10 +98,12 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
       mbar_init(&bars.ring_full[i], 1);
       mbar_init(&bars.ring_empty[i], 1);
     }
+    for (int r = 0; r < Cfg::kRawSlots; ++r) {
+      mbar_init(&bars.k2_full[r], 1);
+      mbar_init(&bars.raw_free[r], 256);  // the soft-max warpgroup (K2 block) and the fold warpgroup (V2 block)
+    }
     for (int x = 0; x < 2; ++x) {
-      mbar_init(&bars.k2_full[x], 1);
       mbar_init(&bars.a_ready[x], 128);
-      mbar_init(&bars.a_free[x], 128);
       mbar_init(&bars.s_ready[x], 1);
       mbar_init(&bars.p_ready[x], 128);
       mbar_init(&bars.o_done[x], 1);
@@ -136,8 +146,6 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
   auto fill_tile = [&](const Walk& w, BandTile& t) {
     t.kb0 = w.klo + kRK * w.b;
     t.jlo = max(0, max(t.kb0 - p.kkl, w.q_first - p.k1w));
-    const int jhi = min(w.q_last, t.kb0 + kRK - 1 + p.kkr);
-    t.nks = min(8, max(1, (jhi - t.jlo + 16) / 16));
     t.first = w.b == 0;
     t.last = w.b == w.nb - 1;
   };
@@ -160,6 +168,7 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
     if (lane == 0) {
       tma_prefetch_desc(&tmK1);
       tma_prefetch_desc(&tmK2b);
+      tma_prefetch_desc(&tmV2b);
       tma_prefetch_desc(&tmSV1);
       uint32_t pos = 0;
       bool alive = true;
@@ -173,13 +182,16 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
         return true;
       };
       for_each_tile([&](const BandTile& t, uint32_t ti) {
-        const int x = ti & 1;
-        const uint32_t u = ti >> 1;
-        if (!mbar_wait(&bars.a_free[x], (u & 1) ^ 1, abort_flag)) return alive = false;
-        mbar_arrive_expect_tx(&bars.k2_full[x], Cfg::kRawBytes);
-        for (int hh = 0; hh < KH; ++hh)
-          tma_load_3d(smem + Cfg::kOffRaw + x * Cfg::kRawBytes + hh * (kRK * 128), &tmK2b, &bars.k2_full[x], hh * 64,
-                      t.kb0, t.bh);
+        const int rs = ti % Cfg::kRawSlots;
+        const uint32_t ru = ti / Cfg::kRawSlots;
+        // the block this slot held four tiles ago has been turned into its operand
+        if (!mbar_wait(&bars.raw_free[rs], (ru & 1) ^ 1, abort_flag)) return alive = false;
+        mbar_arrive_expect_tx(&bars.k2_full[rs], Cfg::kRawBytes);
+        for (int hh = 0; hh < KH; ++hh) {
+          uint8_t* dst = smem + Cfg::kOffRaw + rs * Cfg::kRawBytes + hh * (kRK * 128);
+          tma_load_3d(dst, &tmK2b, &bars.k2_full[rs], hh * 64, t.kb0, t.bh);
+          tma_load_3d(dst + Cfg::kBlockBytes, &tmV2b, &bars.k2_full[rs], hh * 64, t.kb0, t.bh);
+        }
         if (!load_stage(&tmK1, t.jlo, t.bh)) return alive = false;
         if (!load_stage(&tmSV1, t.jlo, t.bh)) return alive = false;
         return true;
@@ -206,10 +218,9 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
       const uint32_t ringK = desc_lo(smem_u32(smem + Cfg::kOffRing), 16);      // K-major view of a stage
       const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), 16384);  // row-major (MN-major) view
       bool alive = true;
-      int prev_nks = 0;
       uint32_t n_tiles = 0;
       // acc_x = P_x * SiLU(V1)slab for tile tt (P_x overlays the first 64 columns of S_x)
-      auto issue_pv = [&](uint32_t tt, int nks) -> bool {
+      auto issue_pv = [&](uint32_t tt) -> bool {
         const int x = tt & 1;
         const uint32_t u = tt >> 1, pos = 2 * tt + 1;
         if (!mbar_wait(&bars.p_ready[x], u & 1, abort_flag)) return false;
@@ -218,7 +229,10 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
         if (!mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag)) return false;
         tc_fence_after();
         const uint32_t bLo = ringMN + (pos % NS) * kTile16;
-        for (int k = 0; k < nks; ++k)
+        // (always the full chain of 8: columns of P beyond the attended range are zero, and a loop with a run-time
+        //  bound costs the issuing thread more than the skipped instructions save)
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
           mma_ts_lo(tmem + Cfg::kTmemAcc + x * D, tmem + x * 128 + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv, k > 0);
         mma_commit(&bars.o_done[x]);
         mma_commit(&bars.ring_empty[pos % NS]);
@@ -238,12 +252,11 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
         }
         mma_commit(&bars.s_ready[x]);
         mma_commit(&bars.ring_empty[pos % NS]);
-        if (ti > 0 && !issue_pv(ti - 1, prev_nks)) return alive = false;
-        prev_nks = t.nks;
+        if (ti > 0 && !issue_pv(ti - 1)) return alive = false;
         n_tiles = ti + 1;
         return true;
       });
-      if (alive && n_tiles > 0) issue_pv(n_tiles - 1, prev_nks);
+      if (alive && n_tiles > 0) issue_pv(n_tiles - 1);
     }
   } else if (warp >= 4 && warp < 12) {
     // ------------------------------------------------------------------ soft-max warpgroups
@@ -254,7 +267,6 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
     const uint32_t tS = tmem + lane_base + x * 128;
     float* stats = (float*)(smem + Cfg::kOffStats) + x * 256;
     uint8_t* Ax = smem + Cfg::kOffA + x * Cfg::kTileA;
-    const uint8_t* raw = smem + Cfg::kOffRaw + x * Cfg::kRawBytes;
     bool alive = true;
     for_each_tile([&](const BandTile& t, uint32_t ti) {
       if ((int)(ti & 1) != x) return true;
@@ -263,8 +275,11 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
       const bool q_ok = g < t.count;
       const T16* Qrow = (const T16*)p.q + ((size_t)t.bh * T + (q_ok ? q_g : t.q0)) * D;
       // ---- operand formation: A[r, :] = s * Q[q_g, :] (.) K2[k_i, :]   (this thread's whole row)
-      alive = __all_sync(0xffffffffu, mbar_wait(&bars.k2_full[x], u & 1, abort_flag));
+      const int rs = ti % Cfg::kRawSlots;
+      const uint8_t* raw = smem + Cfg::kOffRaw + rs * Cfg::kRawBytes;
+      alive = __all_sync(0xffffffffu, mbar_wait(&bars.k2_full[rs], (ti / Cfg::kRawSlots) & 1, abort_flag));
       if (!alive) return false;
+      // (the operand buffer is free: this warpgroup has waited for the slot's previous score product, below)
       float nrm = 0.f;
 #pragma unroll
       for (int cc = 0; cc < D / 8; ++cc) {
@@ -284,6 +299,7 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
       }
       fence_async_smem();
       mbar_arrive(&bars.a_ready[x]);
+      mbar_arrive(&bars.raw_free[rs]);  // the K2 block is consumed
       // columns this row attends: [c_lo, c_hi] (empty for a row outside its query's K2 range)
       const bool in_k = q_ok && k_i <= q_g && q_g - k_i <= p.k2w;
       const int c_lo = max(q_g - p.k1w, k_i - p.kkl);
@@ -294,56 +310,69 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
       alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x], u & 1, abort_flag));
       if (!alive) return false;
       tc_fence_after();
-      mbar_arrive(&bars.a_free[x]);  // the score product has read A and the K2 block is consumed
       // Score bound of the row, |A_row| max_j |K1_j| (log2 units): where it is small for the whole warp it serves as
       // the soft-max reference (P stays a normal number of the 16-bit type) and the row-maximum pass is skipped.
       const float bound = sqrtf(nrm) * k1_max;
       const bool fast = __all_sync(0xffffffffu, bound <= p.bound_limit);
       const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 127);
+      // 32-column chunks no row of the warp attends are not read at all (the band leaves a quarter of the slab empty)
+      int wlo = lo, whi = hi;
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) {
+        wlo = min(wlo, __shfl_xor_sync(0xffffffffu, wlo, o));
+        whi = max(whi, __shfl_xor_sync(0xffffffffu, whi, o));
+      }
       float m_used = bound;
       if (!fast) {
         float mx = -INFINITY;
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          uint32_t sr[64];
-          tmem_ld64(tS + hf * 64, sr);
+        for (int ch = 0; ch < 4; ++ch) {
+          if (ch * 32 + 31 < wlo || ch * 32 > whi) continue;
+          uint32_t sr[32];
+          tmem_ld32(tS + ch * 32, sr);
           tmem_wait_ld();
-          const int l2 = lo - hf * 64, h2 = hi - hf * 64;
+          const int l2 = lo - ch * 32, h2 = hi - ch * 32;
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
+          for (int c = 0; c < 32; ++c)
             if (c >= l2 && c <= h2) mx = fmaxf(mx, __uint_as_float(sr[c]));
         }
         m_used = mx;  // -inf for a row that attends nothing: every P below is then selected to 0
       }
       float psum = 0.f;
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t sr[64];
-        tmem_ld64(tS + hf * 64, sr);
-        tmem_wait_ld();
-        uint32_t pk[32];
-        if (full) {
-          float ps0 = 0.f, ps1 = 0.f;
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[16];
+        if (ch * 32 + 31 < wlo || ch * 32 > whi) {
 #pragma unroll
-          for (int c = 0; c < 64; c += 2) {
-            const float p0 = exp2f(__uint_as_float(sr[c]) - m_used);
-            const float p1 = exp2f(__uint_as_float(sr[c + 1]) - m_used);
-            ps0 += p0;
-            ps1 += p1;
-            pk[c >> 1] = pack2<T16>(p0, p1);
-          }
-          psum += ps0 + ps1;
+          for (int c = 0; c < 16; ++c) pk[c] = 0u;
         } else {
-          const int l2 = lo - hf * 64, h2 = hi - hf * 64;
+          uint32_t sr[32];
+          tmem_ld32(tS + ch * 32, sr);
+          tmem_wait_ld();
+          if (full) {
+            float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-          for (int c = 0; c < 64; c += 2) {
-            const float p0 = (c >= l2 && c <= h2) ? exp2f(__uint_as_float(sr[c]) - m_used) : 0.f;
-            const float p1 = (c + 1 >= l2 && c + 1 <= h2) ? exp2f(__uint_as_float(sr[c + 1]) - m_used) : 0.f;
-            psum += p0 + p1;
-            pk[c >> 1] = pack2<T16>(p0, p1);
+            for (int c = 0; c < 32; c += 2) {
+              const float p0 = exp2f(__uint_as_float(sr[c]) - m_used);
+              const float p1 = exp2f(__uint_as_float(sr[c + 1]) - m_used);
+              ps0 += p0;
+              ps1 += p1;
+              pk[c >> 1] = pack2<T16>(p0, p1);
+            }
+            psum += ps0 + ps1;
+          } else {
+            const int l2 = lo - ch * 32, h2 = hi - ch * 32;
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              const float p0 = (c >= l2 && c <= h2) ? exp2f(__uint_as_float(sr[c]) - m_used) : 0.f;
+              const float p1 = (c + 1 >= l2 && c + 1 <= h2) ? exp2f(__uint_as_float(sr[c + 1]) - m_used) : 0.f;
+              psum += p0 + p1;
+              pk[c >> 1] = pack2<T16>(p0, p1);
+            }
           }
         }
-        tmem_st32(tS + hf * 32, pk);
+        // P chunk ch -> columns [16 ch, 16 ch + 16) of S_x, which the chunks before have already read
+        tmem_st16(tS + ch * 16, pk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -392,7 +421,9 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
       alive = __all_sync(0xffffffffu, mbar_wait(&bars.o_done[x], u & 1, abort_flag));
       if (!alive) return false;
       tc_fence_after();
-      const T16* V2row = (const T16*)p.v2 + ((size_t)t.bh * T + min(k_i, T - 1)) * D;
+      // the V2 rows of the block came in with its K2 rows (the fetch completed before the operand was formed)
+      const int rs = ti % Cfg::kRawSlots;
+      const uint8_t* v2blk = smem + Cfg::kOffRaw + rs * Cfg::kRawBytes + Cfg::kBlockBytes;
       float Ot[D / 32];
 #pragma unroll
       for (int ch = 0; ch < D / 32; ++ch) {
@@ -401,7 +432,8 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
         float v[32];
 #pragma unroll
         for (int i4 = 0; i4 < 4; ++i4) {
-          const uint4 vv = __ldg(reinterpret_cast<const uint4*>(V2row + ch * 32 + i4 * 8));
+          const int cc = ch * 4 + i4;  // 16-byte chunk of the row
+          const uint4 vv = *reinterpret_cast<const uint4*>(v2blk + (cc >> 3) * (kRK * 128) + swz128(lane, cc & 7));
           const uint32_t wv[4] = {vv.x, vv.y, vv.z, vv.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -412,9 +444,11 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
         }
         tmem_wait_ld();
         if (ch == D / 32 - 1) {
-          // the accumulator and the statistics of this slot are in registers: both may be overwritten
+          // the accumulator and the statistics of this slot are in registers: both may be overwritten, and so may
+          // the block slot (its V2 rows have been read)
           tc_fence_before();
           mbar_arrive(&bars.o_free[x]);
+          mbar_arrive(&bars.raw_free[rs]);
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] *= __uint_as_float(o[i]);
@@ -449,16 +483,16 @@ template <int D, typename T16>
 int launch_band(const TdpArgs& a, const void* sv1, const float* k1n) {
   using Cfg = BandCfg<D>;
   const int BN = a.B * a.N;
-  CUtensorMap tmK1, tmK2b, tmSV1;
+  CUtensorMap tmK1, tmK2b, tmV2b, tmSV1;
   int rc;
   if ((rc = make_tmap_3d(&tmK1, a.k1, 2, D, a.T, BN, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tmSV1, sv1, 2, D, a.T, BN, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tmK2b, a.k2, 2, D, a.T, BN, 64, kRK))) return rc;
+  if ((rc = make_tmap_3d(&tmV2b, a.v2, 2, D, a.T, BN, 64, kRK))) return rc;
   BandParams p{};
   p.out = a.out_o;
   p.lse = a.out_lse;
   p.q = a.q;
-  p.v2 = a.v2;
   p.T = a.T;
   p.BN = BN;
   p.q_mod = a.q_mod;
@@ -478,7 +512,7 @@ int launch_band(const TdpArgs& a, const void* sv1, const float* k1n) {
   TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
   const long items = (long)p.n_groups * BN;
   const int grid = (int)(items < num_sms() ? items : num_sms());
-  kern<<<grid, kBandThreads, Cfg::kSmem, a.stream>>>(tmK1, tmK2b, tmSV1, p);
+  kern<<<grid, kBandThreads, Cfg::kSmem, a.stream>>>(tmK1, tmK2b, tmV2b, tmSV1, p);
   count_launch();
   TRITT_CUDA_OK(cudaGetLastError());
   return 0;
