@@ -268,6 +268,25 @@ def reference_kernel_worker():
             step()
             torch.cuda.synchronize()
             res["fwd_bwd_2x8x512x64_fp16_full"] = {"generic_ms": _timed(step, iters=3)}
+    # dot-product-sum, config 3 (the reference's TrittentionTriton module, forward and forward + backward)
+    try:
+        from flash_trittention import TrittentionTriton as RefDps
+
+        ins = [x.to(dev) for x in _make_inputs(2, 8, 1024, 64, 1.0, 4, torch.float16)]
+        mod = RefDps(causal=True, softmax_scale=1 / 8, k_diff=1024)
+
+        def dps_step():
+            leaves = [x.detach().requires_grad_(True) for x in ins[:5]]
+            o, _ = mod(*leaves)
+            o.backward(ins[5])
+
+        dps_step()
+        torch.cuda.synchronize()
+        with torch.no_grad():
+            fwd = bench(lambda: mod(*ins[:5]))
+        res["dps_2x8x1024x64_fp16"] = {"fwd_ms": fwd, "fwd_bwd_ms": _timed(dps_step, iters=3)}
+    except Exception as exc:  # the triple-dot-product timings above stand on their own
+        res["dps_2x8x1024x64_fp16"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}
     print("REFJSON " + json.dumps(res), flush=True)
 
 
