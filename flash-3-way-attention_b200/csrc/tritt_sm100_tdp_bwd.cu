@@ -55,7 +55,7 @@ template <int D> struct BwdCfg {
   static constexpr int kOffVec = kOffDq + D * 4;                 // [2 parities][2][D] fp32: Q[q], dO[q]
   static constexpr int kOffMisc = kOffVec + 4 * D * 4;           // [4] fp32: Dq partials
   static constexpr int kOffBars = kOffMisc + 16;                 // barriers (no static shared memory is used, so
-  static constexpr int kSmem = kOffBars + 192;                   //  the dynamic region starts 1024-byte aligned)
+  static constexpr int kSmem = kOffBars + 208;                   //  the dynamic region starts 1024-byte aligned)
   static constexpr int kTmemS = 0, kTmemDP = 128, kTmemG = 256, kTmemU = 256 + D;
 };
 
@@ -79,7 +79,7 @@ struct BwdParams {
 
 struct BwdBarriers {
   uint64_t ring_full[4], ring_empty[4];
-  uint64_t xy_full, a_ready, a_free;
+  uint64_t xy_full, ax_ready, ay_ready, a_free;  // A (score operand) and A' (dP operand) become ready separately
   uint64_t s_ready, dp_ready, p_ready[2], ds_ready;  // slab hand-offs (P in two column halves)
   uint64_t gu_done, u_free, g_free;               // tile hand-offs with the fold warpgroup (U is drained first)
   uint64_t sm_sync, fold_sync;
@@ -116,7 +116,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   constexpr int kFoldWarp0 = BwdThreads<NSW>::kFoldWarp0;
   constexpr int CW = kBC / NSW;  // slab columns owned by one soft-max warpgroup
   extern __shared__ __align__(1024) uint8_t smem[];
-  static_assert(sizeof(BwdBarriers) <= 192, "barrier block too large");
+  static_assert(sizeof(BwdBarriers) <= 208, "barrier block too large");
   BwdBarriers& bars = *reinterpret_cast<BwdBarriers*>(smem + Cfg::kOffBars);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (smem_u32(smem) & 1023u) {
@@ -132,7 +132,8 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       mbar_init(&bars.ring_empty[i], 1);
     }
     mbar_init(&bars.xy_full, 1);
-    mbar_init(&bars.a_ready, kNumSoftmax);
+    mbar_init(&bars.ax_ready, kNumSoftmax);
+    mbar_init(&bars.ay_ready, kNumSoftmax);
     mbar_init(&bars.a_free, kNumSoftmax);
     mbar_init(&bars.s_ready, 1);
     mbar_init(&bars.dp_ready, 1);
@@ -161,10 +162,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   const int T = p.T;
   const long n_items = (long)p.nq * p.BN * 2;
 
-  // item -> (role, head, query); late (expensive) queries first
+  // item -> (role, head, query); late (expensive) queries first.  Items 2r and 2r + 1 are the two roles of one (head,
+  // query); which of them is which alternates with r in blocks of half the grid, so that the items of one CTA
+  // (gridDim.x apart) alternate between the roles: role-0 tiles cost more (their fold also forms dQ), and a CTA
+  // that only ever saw one role would finish 6 % later than its neighbour.
   auto decode = [&](long item, int& role, int& bh, int& q) {
-    role = (int)(item & 1);
     const long r = item >> 1;
+    role = (int)((item ^ (r / ((gridDim.x + 1) >> 1))) & 1);
     bh = (int)(r % p.BN);
     q = p.q_rem + (p.nq - 1 - (int)(r / p.BN)) * p.q_mod;
   };
@@ -228,13 +232,16 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
           int c0, ncs;
           c_range(q, win, xt, c0, ncs);
-          if (!mbar_wait(&bars.a_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+          // the tile's first key / value slab does not depend on the operand buffers: fetch it before waiting for them
+          alive = load_stage(tmKc, c0 * kBC, bh);
+          if (alive) alive = load_stage(tmVc, c0 * kBC, bh);
+          if (!alive || !mbar_wait(&bars.a_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
           mbar_arrive_expect_tx(&bars.xy_full, 2 * Cfg::kTileA);
           for (int hh = 0; hh < KH; ++hh) {
             tma_load_3d(smem + Cfg::kOffA + hh * 16384, tmX, &bars.xy_full, hh * 64, xt * 128, bh);
             tma_load_3d(smem + Cfg::kOffA2 + hh * 16384, tmY, &bars.xy_full, hh * 64, xt * 128, bh);
           }
-          for (int c = c0; c < c0 + ncs && alive; ++c) {
+          for (int c = c0 + 1; c < c0 + ncs && alive; ++c) {
             alive = load_stage(tmKc, c * kBC, bh);
             if (alive) alive = load_stage(tmVc, c * kBC, bh);
           }
@@ -324,9 +331,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
           int c0, ncs;
           c_range(q, win, xt, c0, ncs);
-          if (!mbar_wait(&bars.a_ready, xt_count & 1, abort_flag)) { alive = false; break; }
+          // the first score product starts while the soft-max warps still form the dP operand
+          if (!mbar_wait(&bars.ax_ready, xt_count & 1, abort_flag)) { alive = false; break; }
           tc_fence_after();
-          if (!issue_s(base) || !issue_dp(base + 1)) { alive = false; break; }
+          if (!issue_s(base)) { alive = false; break; }
+          if (!mbar_wait(&bars.ay_ready, xt_count & 1, abort_flag)) { alive = false; break; }
+          tc_fence_after();
+          if (!issue_dp(base + 1)) { alive = false; break; }
           for (int c = 0; c < ncs && alive; ++c, ++n) {
             const bool more = c + 1 < ncs;
             if (!mbar_wait(&bars.p_ready[0], n & 1, abort_flag)) { alive = false; break; }
@@ -409,25 +420,41 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         // ---- operand formation (in place): A = scale2*Q[q] (.) X tile,  A' = dO[q] (.) Y tile
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.xy_full, xt_count & 1, abort_flag));
         if (!alive) break;
+        // (each warpgroup takes half of the columns; the eight Q / dO values of a 16-byte chunk are the same for all rows)
 #pragma unroll
         for (int ci = 0; ci < D / 8 / NSW; ++ci) {
           const int cc = wg * (D / 8 / NSW) + ci;
           const uint32_t off = (cc >> 3) * 16384 + swz128(row, cc & 7);
-          uint4 xv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA + off);
-          uint4 yv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA2 + off);
-          uint32_t wx[4] = {xv.x, xv.y, xv.z, xv.w}, wy[4] = {yv.x, yv.y, yv.z, yv.w};
+          const uint4 xv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA + off);
+          const float4 q0 = *reinterpret_cast<const float4*>(qv + cc * 8), q1 = *reinterpret_cast<const float4*>(qv + cc * 8 + 4);
+          const float qf[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+          uint32_t wx[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int h = cc * 8 + 2 * e;
-            const float2 fx = unpack2<T16>(wx[e]), fy = unpack2<T16>(wy[e]);
-            wx[e] = pack2<T16>(fx.x * (scale2 * qv[h]), fx.y * (scale2 * qv[h + 1]));
-            wy[e] = pack2<T16>(fy.x * dov[h], fy.y * dov[h + 1]);
+            const float2 fx = unpack2<T16>(wx[e]);
+            wx[e] = pack2<T16>(fx.x * (scale2 * qf[2 * e]), fx.y * (scale2 * qf[2 * e + 1]));
           }
           *reinterpret_cast<uint4*>(smem + Cfg::kOffA + off) = make_uint4(wx[0], wx[1], wx[2], wx[3]);
+        }
+        fence_async_smem();
+        mbar_arrive(&bars.ax_ready);
+#pragma unroll
+        for (int ci = 0; ci < D / 8 / NSW; ++ci) {
+          const int cc = wg * (D / 8 / NSW) + ci;
+          const uint32_t off = (cc >> 3) * 16384 + swz128(row, cc & 7);
+          const uint4 yv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA2 + off);
+          const float4 d0 = *reinterpret_cast<const float4*>(dov + cc * 8), d1 = *reinterpret_cast<const float4*>(dov + cc * 8 + 4);
+          const float df[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+          uint32_t wy[4] = {yv.x, yv.y, yv.z, yv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 fy = unpack2<T16>(wy[e]);
+            wy[e] = pack2<T16>(fy.x * df[2 * e], fy.y * df[2 * e + 1]);
+          }
           *reinterpret_cast<uint4*>(smem + Cfg::kOffA2 + off) = make_uint4(wy[0], wy[1], wy[2], wy[3]);
         }
         fence_async_smem();
-        mbar_arrive(&bars.a_ready);
+        mbar_arrive(&bars.ay_ready);
 
         // columns this row sees: [c_lo, c_hi] (empty for a row outside its own range: its P is zero)
         const int x_r = xt * 128 + row;
