@@ -59,6 +59,22 @@ def test_c_abi_rejects_bad_arguments_without_a_device():
     # DPS needs a workspace: a missing one is an argument error, not a crash
     dps = [p] * 7 + [1, 1, 8, 16, _native.F32, 0.125, 1, 8, None, 0, None, 0, None]
     assert lib.tritt_dps_fwd(*dps) == -6
+    # windows are distances: a negative one is refused under a causal mask (the reference would apply it literally
+    # and leave rows without anything to attend), and ignored without one
+    neg = args(16, _native.F32)
+    neg[14] = -1  # k1_window
+    assert lib.tritt_tdp_fwd(*neg) == -10
+    assert b"window" in lib.tritt_last_error()
+    dps_neg = [p] * 7 + [1, 1, 8, 16, _native.F32, 0.125, 1, -2, None, 0, None, 0, None]
+    assert lib.tritt_dps_fwd(*dps_neg) == -10
+    # B*N is a grid dimension of the CUDA-core kernels
+    big = args(16, _native.F32)
+    big[7], big[8] = 256, 257
+    assert lib.tritt_tdp_fwd(*big) == -11
+    assert b"65535" in lib.tritt_last_error()
+    # the saved-state backward refuses a missing forward workspace
+    saved = [p] * 13 + [1, 1, 8, 16, _native.F32, 0.125, 1, 8, p, 1 << 20, None, 0, None, 0, None]
+    assert lib.tritt_dps_bwd_saved(*saved) == -4
 
 
 def test_tdp_path_selection():
