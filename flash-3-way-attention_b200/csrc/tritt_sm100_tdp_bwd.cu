@@ -475,11 +475,15 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           if (!alive) break;
           tc_fence_after();
           static_assert(CW == 64, "the two-half hand-off of P is written for two soft-max warpgroups");
+          // (the read of the second half is in flight while the first half is worked on)
+          uint32_t sh[2][32];
+          tmem_ld32(tS, sh[0]);
+          tmem_wait_ld();
+          tmem_ld32(tS + 32, sh[1]);
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
-            uint32_t s[32];
-            tmem_ld32(tS + hf * 32, s);
-            tmem_wait_ld();
+            if (hf == 1) tmem_wait_ld();
+            const uint32_t(&s)[32] = sh[hf];
             const int l2 = lo - hf * 32, h2 = hi - hf * 32;
             if (l2 <= 0 && h2 >= 31) {
 #pragma unroll
