@@ -395,12 +395,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       alive = __all_sync(0xffffffffu,
                          mbar_wait(&bars.vec_free[item_count & 1], ((item_count >> 1) & 1) ^ 1, abort_flag));
       if (!alive) break;
+      const float scale2 = p.alpha * kLog2e;
       if (wg == 0) {
         float dq_part = 0.f;
         if (row < D) {
           const float qf = to_f(((const T16*)p.q)[hb + (size_t)q * D + row]);
           const float dof = to_f(((const T16*)p.d_o)[hb + (size_t)q * D + row]);
-          qv[row] = qf;
+          qv[row] = qf * scale2;   // (pre-scaled: the score operand is scale2 * Q[q] (.) X)
           dov[row] = dof;
           dq_part = dof * to_f(((const T16*)p.o)[hb + (size_t)q * D + row]);
         }
@@ -412,7 +413,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       const float Dq = misc[0] + misc[1] + misc[2] + misc[3];
       // (minus the fp16 range shift: P below is the probability times 2^e)
       const float lse2 = p.lse[(size_t)bh * T + q] * kLog2e - (float)prob_shift<T16>(q, p.causal, T, p.k1w, p.k2w);
-      const float scale2 = p.alpha * kLog2e;
+      const float2 nlse = make_float2(-lse2, -lse2), ndq = make_float2(-Dq, -Dq);
 
       for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
         int c0, ncs;
@@ -427,12 +428,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           const uint32_t off = (cc >> 3) * 16384 + swz128(row, cc & 7);
           const uint4 xv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA + off);
           const float4 q0 = *reinterpret_cast<const float4*>(qv + cc * 8), q1 = *reinterpret_cast<const float4*>(qv + cc * 8 + 4);
-          const float qf[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+          const float2 qf[4] = {make_float2(q0.x, q0.y), make_float2(q0.z, q0.w), make_float2(q1.x, q1.y),
+                                make_float2(q1.z, q1.w)};
           uint32_t wx[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float2 fx = unpack2<T16>(wx[e]);
-            wx[e] = pack2<T16>(fx.x * (scale2 * qf[2 * e]), fx.y * (scale2 * qf[2 * e + 1]));
+            const float2 a2 = __fmul2_rn(unpack2<T16>(wx[e]), qf[e]);
+            wx[e] = pack2<T16>(a2.x, a2.y);
           }
           *reinterpret_cast<uint4*>(smem + Cfg::kOffA + off) = make_uint4(wx[0], wx[1], wx[2], wx[3]);
         }
@@ -444,12 +446,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           const uint32_t off = (cc >> 3) * 16384 + swz128(row, cc & 7);
           const uint4 yv = *reinterpret_cast<const uint4*>(smem + Cfg::kOffA2 + off);
           const float4 d0 = *reinterpret_cast<const float4*>(dov + cc * 8), d1 = *reinterpret_cast<const float4*>(dov + cc * 8 + 4);
-          const float df[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+          const float2 df[4] = {make_float2(d0.x, d0.y), make_float2(d0.z, d0.w), make_float2(d1.x, d1.y),
+                                make_float2(d1.z, d1.w)};
           uint32_t wy[4] = {yv.x, yv.y, yv.z, yv.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float2 fy = unpack2<T16>(wy[e]);
-            wy[e] = pack2<T16>(fy.x * df[2 * e], fy.y * df[2 * e + 1]);
+            const float2 a2 = __fmul2_rn(unpack2<T16>(wy[e]), df[e]);
+            wy[e] = pack2<T16>(a2.x, a2.y);
           }
           *reinterpret_cast<uint4*>(smem + Cfg::kOffA2 + off) = make_uint4(wy[0], wy[1], wy[2], wy[3]);
         }
@@ -486,10 +489,12 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             const uint32_t(&s)[32] = sh[hf];
             const int l2 = lo - hf * 32, h2 = hi - hf * 32;
             if (l2 <= 0 && h2 >= 31) {
+              // (packed fp32 pairs: one subtraction per two scores)
 #pragma unroll
-              for (int i = 0; i < 32; i += 2)
-                pk[hf * 16 + (i >> 1)] = pack2<T16>(exp2f(__uint_as_float(s[i]) - lse2),
-                                                    exp2f(__uint_as_float(s[i + 1]) - lse2));
+              for (int i = 0; i < 32; i += 2) {
+                const float2 x = __fadd2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), nlse);
+                pk[hf * 16 + (i >> 1)] = pack2<T16>(exp2f(x.x), exp2f(x.y));
+              }
             } else {
 #pragma unroll
               for (int i = 0; i < 32; i += 2) {
@@ -520,8 +525,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < CW; i += 2) {
-              const float2 pp = unpack2<T16>(pk[i >> 1]);
-              dk[i >> 1] = pack2<T16>(pp.x * (__uint_as_float(dp[i]) - Dq), pp.y * (__uint_as_float(dp[i + 1]) - Dq));
+              const float2 d = __fadd2_rn(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), ndq);
+              const float2 ds = __fmul2_rn(unpack2<T16>(pk[i >> 1]), d);
+              dk[i >> 1] = pack2<T16>(ds.x, ds.y);
             }
           }
           tmem_st(tDP, dk);  // dS -> first half of this warpgroup's dP columns
@@ -601,14 +607,20 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           float v[32];
           {
             const float4* mul = reinterpret_cast<const float4*>((is_u ? dov : qv) + h0);
-            const float sc = is_u ? unshift : alpha_u;
+            // (the Q copy carries the factor alpha * log2(e) of the score operand)
+            const float sc = is_u ? unshift : unshift * (1.f / kLog2e);
+            const float2 sc2 = make_float2(sc, sc);
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               const float4 m = mul[i4];
-              v[i4 * 4] = sc * __uint_as_float(g[i4 * 4]) * m.x;
-              v[i4 * 4 + 1] = sc * __uint_as_float(g[i4 * 4 + 1]) * m.y;
-              v[i4 * 4 + 2] = sc * __uint_as_float(g[i4 * 4 + 2]) * m.z;
-              v[i4 * 4 + 3] = sc * __uint_as_float(g[i4 * 4 + 3]) * m.w;
+              const float2 lo = __fmul2_rn(__fmul2_rn(make_float2(__uint_as_float(g[i4 * 4]), __uint_as_float(g[i4 * 4 + 1])), sc2),
+                                           make_float2(m.x, m.y));
+              const float2 hi = __fmul2_rn(__fmul2_rn(make_float2(__uint_as_float(g[i4 * 4 + 2]), __uint_as_float(g[i4 * 4 + 3])), sc2),
+                                           make_float2(m.z, m.w));
+              v[i4 * 4] = lo.x;
+              v[i4 * 4 + 1] = lo.y;
+              v[i4 * 4 + 2] = hi.x;
+              v[i4 * 4 + 3] = hi.y;
             }
           }
           if (pc == D / 32 - 1) {
@@ -643,9 +655,12 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
               const uint32_t wx[4] = {xr[i4].x, xr[i4].y, xr[i4].z, xr[i4].w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const float2 f = unpack2<T16>(wx[e]);
-                v[i4 * 8 + 2 * e] = alpha_u * __uint_as_float(g[i4 * 8 + 2 * e]) * f.x;
-                v[i4 * 8 + 2 * e + 1] = alpha_u * __uint_as_float(g[i4 * 8 + 2 * e + 1]) * f.y;
+                const float2 gx = __fmul2_rn(__fmul2_rn(make_float2(__uint_as_float(g[i4 * 8 + 2 * e]),
+                                                                    __uint_as_float(g[i4 * 8 + 2 * e + 1])),
+                                                        make_float2(alpha_u, alpha_u)),
+                                             unpack2<T16>(wx[e]));
+                v[i4 * 8 + 2 * e] = gx.x;
+                v[i4 * 8 + 2 * e + 1] = gx.y;
               }
             }
             const float colsum = warp_transpose_sum(v, lane);

@@ -18,8 +18,10 @@
 //                acc_x += P_x*SiLU(V1) with P_x read from TMEM (it overlays S_x) and the value tile used
 //                row-major (MN-major descriptor).  128-column slabs keep every accumulation chain at
 //                8 instructions of 128x128x16, the shape the pipe runs at full rate.
-//   warps 4-7    soft-max warpgroup of tile a (one row per thread), warps 8-11 of tile b: row max,
-//                exp2 with lazy rescaling, P written back to TMEM as 16-bit; they also form A_a, A_b
+//   warps 4-11   two soft-max warpgroups that work on the same slab, tile a then tile b, 64 of its 128 columns
+//                each (one row per thread): exp2 against the row's score bound, or, where that is too large,
+//                row max (exchanged between the two warps that share the rows) and lazy rescaling; P written
+//                back to TMEM as 16-bit over the first half of the columns just read; they also form A_a, A_b
 //   warps 12-15  fold warpgroup: when a k-tile is finished, folds acc_x (times V2, soft-max over k) into
 //                the queries' running (max, sum, output) while the other warps start the next k-tile
 // Causal structure: for a fixed query the mask is "j <= q" on columns and "k <= q" on rows, so
@@ -45,11 +47,12 @@ template <int D> struct FwdCfg {
   static constexpr int kOffAa = 0;
   static constexpr int kOffAb = kTileA;
   static constexpr int kOffRing = 2 * kTileA;
-  static constexpr int kOffStats = kOffRing + kStages * kTileA;  // [2 parities][2 tiles][128][2] fp32: row (max, sum)
-  static constexpr int kOffRed = kOffStats + 2 * 2 * 128 * 2 * 4;  // [2 tiles][4 warps][D] fp32 column sums
+  static constexpr int kOffStats = kOffRing + kStages * kTileA;  // [2 parities][2 tiles][128][4] fp32: row (reference, two partial sums, -)
+  static constexpr int kOffRed = kOffStats + 2 * 2 * 128 * 4 * 4;  // [2 tiles][4 warps][D] fp32 column sums
   static constexpr int kOffFstat = kOffRed + 2 * 4 * D * 4;        // [2 tiles][8] fp32 warp max / sum
   static constexpr int kOffNorm = kOffFstat + 2 * 8 * 4;            // [2 tiles][2 column halves][128] fp32: partial |A_row|^2
-  static constexpr int kOffBars = kOffNorm + 2 * 2 * 128 * 4;
+  static constexpr int kOffXchg = kOffNorm + 2 * 2 * 128 * 4;       // [2 slots][2 warpgroups][128] fp32: row maxima being exchanged
+  static constexpr int kOffBars = kOffXchg + 2 * 2 * 128 * 4;
   static constexpr int kSmem = kOffBars + 256;
   static constexpr int kTmemO = 256;  // S_a | S_b | acc_a | acc_b
 };
@@ -72,6 +75,7 @@ struct FwdBarriers {
   uint64_t s_ready[2], p_ready[2];               // per tile, one phase per slab
   uint64_t o_done, o_free[2], stats_ready[2];    // per k-tile hand-offs with the fold warpgroup
   uint64_t fold_sync;
+  uint64_t xchg[4];                              // the two soft-max warps of a lane quadrant, per exchange of row maxima
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -104,10 +108,11 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     mbar_init(&bars.a_free, 256);
     for (int x = 0; x < 2; ++x) {
       mbar_init(&bars.s_ready[x], 1);
-      mbar_init(&bars.p_ready[x], 128);
+      mbar_init(&bars.p_ready[x], 256);
       mbar_init(&bars.o_free[x], 128);
-      mbar_init(&bars.stats_ready[x], 128);
+      mbar_init(&bars.stats_ready[x], 256);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&bars.xchg[i], 64);
     mbar_init(&bars.o_done, 1);
     mbar_init(&bars.fold_sync, 128);
     fence_barrier_init();
@@ -264,16 +269,17 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       auto issue_pv = [&](int x, uint32_t pos, uint32_t acc, int hm) {
         const uint32_t bLo = ringMN + (pos % NS) * kTile16;
         if (hm == 0) {
+          // (P of the slab's column half h sits in the first 32 columns of that half of S_x)
 #pragma unroll
           for (int k = 0; k < kBJ / 16; ++k)
-            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv,
-                      k > 0 ? 1u : acc);
+            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (k >> 2) * 64 + (k & 3) * 8, bLo + k * (2048 >> 4), kHi,
+                      idesc_pv, k > 0 ? 1u : acc);
         } else {
           const uint32_t bRow = bLo + (hm == 2 ? (4 * 2048) >> 4 : 0);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + k * 8, bRow + k * (2048 >> 4), kHi, idesc_pv,
-                      k > 0 ? 1u : acc);
+            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (k >> 1) * 32 + (k & 1) * 8, bRow + k * (2048 >> 4), kHi,
+                      idesc_pv, k > 0 ? 1u : acc);
         }
       };
 
@@ -322,21 +328,90 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     }
   } else if (warp >= 4 && warp < 12) {
     // ------------------------------------------------------------------ soft-max warpgroups
-    const int x = (warp - 4) >> 2;          // tile: 0 = query a, 1 = query b
+    // Both warpgroups work on the same slab, tile a first, then tile b: warpgroup `wg` takes the slab's columns
+    // [wg * 64, wg * 64 + 64) (32 of a half-width slab's 64), one row per thread, and writes P over the first half of
+    // the columns it has read.  While they are on one tile, the tensor pipe runs the other tile's two products.
+    const int wg = (warp - 4) >> 2;         // column half of every slab
     const int wq = warp & 3;                // TMEM lane quadrant of this warp
-    const int row = wq * 32 + lane;         // row of the tile owned by this thread
+    const int row = wq * 32 + lane;         // row of both tiles owned by this thread
     const int st = tid - 128;               // 0..255 over both warpgroups
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     float* stats = (float*)(smem + Cfg::kOffStats);
     float* norms = (float*)(smem + Cfg::kOffNorm);
-    uint32_t kt_count = 0, n = 0;
+    float* xchg = (float*)(smem + Cfg::kOffXchg);
+    uint32_t kt_count = 0, n = 0, xphase = 0;
     bool alive = true;
+
+    // largest score of this thread's NC columns at TMEM address tS ([lo, hi]: the columns the row may see)
+    auto row_max = [&](auto nc, uint32_t tS, bool full, int lo, int hi) -> float {
+      constexpr int NC = decltype(nc)::value;
+      uint32_t sr[NC];
+      if constexpr (NC == 64) tmem_ld64(tS, sr); else tmem_ld32(tS, sr);
+      tmem_wait_ld();
+      float mx = -INFINITY;
+      if (full) {
+        // four independent chains instead of one NC-deep dependency
+        float m0 = __uint_as_float(sr[0]), m1 = __uint_as_float(sr[1]), m2 = __uint_as_float(sr[2]),
+              m3 = __uint_as_float(sr[3]);
+#pragma unroll
+        for (int c = 4; c < NC; c += 4) {
+          m0 = fmaxf(m0, __uint_as_float(sr[c]));
+          m1 = fmaxf(m1, __uint_as_float(sr[c + 1]));
+          m2 = fmaxf(m2, __uint_as_float(sr[c + 2]));
+          m3 = fmaxf(m3, __uint_as_float(sr[c + 3]));
+        }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      } else {
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+          if (c >= lo && c <= hi) mx = fmaxf(mx, __uint_as_float(sr[c]));
+      }
+      return mx;
+    };
+    // P = exp2(S - m) of this thread's NC columns, packed to 16 bits over the first NC / 2 of them; returns their sum
+    auto form_p = [&](auto nc, uint32_t tS, bool full, int lo, int hi, float m) -> float {
+      constexpr int NC = decltype(nc)::value;
+      uint32_t sr[NC];
+      if constexpr (NC == 64) tmem_ld64(tS, sr); else tmem_ld32(tS, sr);
+      tmem_wait_ld();
+      uint32_t pk[NC / 2];
+      float ps0 = 0.f, ps1 = 0.f;
+      if (full) {
+        // packed fp32 pairs: one subtraction and one addition per two scores
+        const float2 nm = make_float2(-m, -m);
+        float2 pa = make_float2(0.f, 0.f), pb = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < NC; c += 4) {
+          const float2 x0 = __fadd2_rn(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), nm);
+          const float2 x1 = __fadd2_rn(make_float2(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), nm);
+          const float2 e0 = make_float2(exp2f(x0.x), exp2f(x0.y));
+          const float2 e1 = make_float2(exp2f(x1.x), exp2f(x1.y));
+          pa = __fadd2_rn(pa, e0);
+          pb = __fadd2_rn(pb, e1);
+          pk[c >> 1] = pack2<T16>(e0.x, e0.y);
+          pk[(c >> 1) + 1] = pack2<T16>(e1.x, e1.y);
+        }
+        ps0 = pa.x + pb.x;
+        ps1 = pa.y + pb.y;
+      } else {
+        // (a row with no valid column so far has m = -inf and selects 0 everywhere)
+#pragma unroll
+        for (int c = 0; c < NC; c += 2) {
+          const float p0 = (c >= lo && c <= hi) ? exp2f(__uint_as_float(sr[c]) - m) : 0.f;
+          const float p1 = (c + 1 >= lo && c + 1 <= hi) ? exp2f(__uint_as_float(sr[c + 1]) - m) : 0.f;
+          ps0 += p0;
+          ps1 += p1;
+          pk[c >> 1] = pack2<T16>(p0, p1);
+        }
+      }
+      tmem_st(tS, pk);
+      return ps0 + ps1;
+    };
 
     for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
       int bh, qa, qb, kt0, nkt;
       decode(item, bh, qa, qb);
       k_range(qa, qb, kt0, nkt);
-      const int qx = x == 0 ? qa : qb;
       const T16* Qg = (const T16*)p.q + (size_t)bh * T * D;
       // largest K1 row norm of this head: with |A_row| it bounds every score of the row (Cauchy-Schwarz)
       const float k1_max = p.k1_norm2_max ? sqrtf(__ldg(p.k1_norm2_max + bh)) : INFINITY;
@@ -345,15 +420,19 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         int jt0, njt, ja, jb;
         j_range(qa, qb, kt, jt0, njt);
         col_span(qa, qb, kt, ja, jb);
-        // Columns this row may see: [c_lo, c_hi].  A row outside the k range of its query (its weight in the
-        // fold is zero) keeps the query's own column range so that it never sees an empty one by construction;
+        // Columns this row may see, per tile: [c_lo, c_hi].  A row outside the k range of its query (its weight in
+        // the fold is zero) keeps the query's own column range so that it never sees an empty one by construction;
         // a row inside can still see none in a slab, or at all: its maximum then stays -inf and its P zero.
-        int c_lo = 0, c_hi = T - 1;
+        int c_lo[2] = {0, 0}, c_hi[2] = {T - 1, T - 1};
         if (p.causal) {
           const int k_r = kt * 128 + row;
-          const bool in_k = k_r <= qx && qx - k_r <= p.k2w;
-          c_lo = max(qx - p.k1w, in_k ? k_r - p.kkl : 0);
-          c_hi = in_k ? min(qx, k_r + p.kkr) : qx;
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int qx = x == 0 ? qa : qb;
+            const bool in_k = k_r <= qx && qx - k_r <= p.k2w;
+            c_lo[x] = max(qx - p.k1w, in_k ? k_r - p.kkl : 0);
+            c_hi[x] = in_k ? min(qx, k_r + p.kkr) : qx;
+          }
         }
         // ---- operand formation: A_a = s*Q[qa] (.) K2tile (in place), A_b = s*Q[qb] (.) K2tile
         alive = __all_sync(0xffffffffu, mbar_wait(&bars.k2_full, kt_count & 1, abort_flag));
@@ -388,8 +467,8 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             *reinterpret_cast<uint4*>(smem + Cfg::kOffAa + off) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
             *reinterpret_cast<uint4*>(smem + Cfg::kOffAb + off) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
           }
-          // (read by both tiles' owners of row r after their first s_ready wait of this k-tile, which this
-          //  thread's a_ready arrival below precedes; rewritten only after both have passed a_free)
+          // (read by both owners of row r after their first s_ready wait of this k-tile, which this thread's
+          //  a_ready arrival below precedes; rewritten only after both have passed a_free)
           norms[(0 * 2 + (st >> 7)) * 128 + r] = na;
           norms[(1 * 2 + (st >> 7)) * 128 + r] = nb;
         }
@@ -397,134 +476,94 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         mbar_arrive(&bars.a_ready);
 
         // ---- walk over the slabs
-        const uint32_t tS = tmem + lane_base + x * kBJ;
-        float m_used = -INFINITY, l_sum = 0.f;
-        bool fast = false;
-        for (int jt = 0; jt < njt; ++jt, ++n) {
-          alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x], n & 1, abort_flag));
-          if (!alive) break;
-          tc_fence_after();
-          if (jt == 0) {
-            // Score bound of this row for the whole k-tile, |A_row| * max_j |K1_j| (log2 units).  Where it is
-            // small for every row of the warp, the bound itself serves as the soft-max reference: P stays
-            // within [2^-2b, 1], representable in the 16-bit type, so the row-maximum pass and every later
-            // rescaling are skipped.
-            const float bound = sqrtf(norms[(x * 2 + 0) * 128 + row] + norms[(x * 2 + 1) * 128 + row]) * k1_max;
-            fast = __all_sync(0xffffffffu, bound <= p.bound_limit);
-            if (fast) m_used = bound;
-          }
-          if (jt == njt - 1) mbar_arrive(&bars.a_free);  // the last score product of this k-tile has read A_x
-          // this row's valid columns within the slab: [lo, hi]; the warp takes the unmasked path when every
-          // row sees the whole slab
+        float m_used[2] = {-INFINITY, -INFINITY}, l_sum[2] = {0.f, 0.f};
+        bool fast[2] = {false, false};
+        for (int jt = 0; jt < njt && alive; ++jt, ++n) {
           // A slab with attended columns in one 64-column half only was computed for that half alone: its scores
           // are in the first 64 columns of S_x and stand for the slab's columns [coff, coff + 64).
           const int hm = halves(ja, jb, (jt0 + jt) * kBJ);
           const int nh = hm ? 1 : 2, coff = hm == 2 ? 64 : 0;
-          const int j0 = (jt0 + jt) * kBJ + coff;
-          const int lo = c_lo - j0, hi = c_hi - j0;
-          const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 64 * nh - 1);
-          // pass 1: row maximum
-          float mx = -INFINITY;
-          if (!fast) {
+          const int cw = 32 * nh;                                  // columns of this warpgroup in this slab
+          const int j0 = (jt0 + jt) * kBJ + coff + wg * cw;      // its first column
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            if (hf >= nh) break;
-            uint32_t sr[64];
-            tmem_ld64(tS + hf * 64, sr);
-            tmem_wait_ld();
-            if (full) {
-              // four independent chains instead of one 64-deep dependency
-              float m0 = __uint_as_float(sr[0]), m1 = __uint_as_float(sr[1]), m2 = __uint_as_float(sr[2]),
-                    m3 = __uint_as_float(sr[3]);
-#pragma unroll
-              for (int c = 4; c < 64; c += 4) {
-                m0 = fmaxf(m0, __uint_as_float(sr[c]));
-                m1 = fmaxf(m1, __uint_as_float(sr[c + 1]));
-                m2 = fmaxf(m2, __uint_as_float(sr[c + 2]));
-                m3 = fmaxf(m3, __uint_as_float(sr[c + 3]));
-              }
-              mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
-            } else {
-              const int l2 = lo - hf * 64, h2 = hi - hf * 64;
-#pragma unroll
-              for (int c = 0; c < 64; ++c)
-                if (c >= l2 && c <= h2) mx = fmaxf(mx, __uint_as_float(sr[c]));
+          for (int x = 0; x < 2; ++x) {
+            alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x], n & 1, abort_flag));
+            if (!alive) break;
+            tc_fence_after();
+            if (jt == 0) {
+              // Score bound of this row for the whole k-tile, |A_row| * max_j |K1_j| (log2 units).  Where it is
+              // small for every row of the warp, the bound itself serves as the soft-max reference: P stays
+              // within [2^-2b, 1], representable in the 16-bit type, so the row-maximum pass and every later
+              // rescaling are skipped.  (The two warps that share these rows decide alike: same data, same code.)
+              const float bound = sqrtf(norms[(x * 2 + 0) * 128 + row] + norms[(x * 2 + 1) * 128 + row]) * k1_max;
+              fast[x] = __all_sync(0xffffffffu, bound <= p.bound_limit);
+              if (fast[x]) m_used[x] = bound;
             }
-          }
-          }
-          if (fast) {
-            // reference fixed for the k-tile
-          } else if (jt == 0) {
-            m_used = mx;  // nothing accumulated yet in this k-tile
-          } else {
-            const bool grow = mx > m_used + kRescaleGap;
-            if (__any_sync(0xffffffffu, grow)) {
-              // some row of this warp moved its max up noticeably: rescale accumulator rows (factor 1
-              // for the rows that did not move).
-              const float corr = grow ? exp2f(m_used - mx) : 1.f;
-              if (grow) {
-                m_used = mx;
-                l_sum *= corr;
-              }
-              // (s_ready of this slab was committed after the previous P*V, so that product has landed)
-              const uint32_t tO = tmem + lane_base + Cfg::kTmemO + x * D;
+            // the last score product of this k-tile has read A_a and A_b
+            if (x == 1 && jt == njt - 1) mbar_arrive(&bars.a_free);
+            const uint32_t tS = tmem + lane_base + x * kBJ + wg * cw;
+            // this row's valid columns among the warpgroup's: [lo, hi]; the warp takes the unmasked code when all its
+            // rows see all of them
+            const int lo = c_lo[x] - j0, hi = c_hi[x] - j0;
+            const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= cw - 1);
+            if (!fast[x]) {
+              // pass 1: row maximum over this warpgroup's columns, then over the slab through the partner warp
+              float mx = nh == 2 ? row_max(std::integral_constant<int, 64>{}, tS, full, lo, hi)
+                                 : row_max(std::integral_constant<int, 32>{}, tS, full, lo, hi);
+              float* slot = xchg + (xphase & 1) * 256;
+              slot[wg * 128 + row] = mx;
+              mbar_arrive(&bars.xchg[wq]);
+              alive = __all_sync(0xffffffffu, mbar_wait(&bars.xchg[wq], xphase & 1, abort_flag));
+              if (!alive) break;
+              mx = fmaxf(mx, slot[(wg ^ 1) * 128 + row]);
+              ++xphase;
+              if (jt == 0) {
+                m_used[x] = mx;  // nothing accumulated yet in this k-tile
+              } else {
+                const bool grow = mx > m_used[x] + kRescaleGap;
+                if (__any_sync(0xffffffffu, grow)) {
+                  // some row of this warp moved its max up noticeably: rescale accumulator rows (factor 1 for the
+                  // rows that did not move); each warpgroup takes half of the accumulator's columns
+                  const float corr = grow ? exp2f(m_used[x] - mx) : 1.f;
+                  if (grow) {
+                    m_used[x] = mx;
+                    l_sum[x] *= corr;
+                  }
+                  // (s_ready of this slab was committed after the previous P*V, so that product has landed)
+                  const uint32_t tO = tmem + lane_base + Cfg::kTmemO + x * D + wg * (D / 2);
 #pragma unroll
-              for (int ch = 0; ch < D / 32; ++ch) {
-                uint32_t o[32];
-                tmem_ld32(tO + ch * 32, o);
-                tmem_wait_ld();
+                  for (int ch = 0; ch < D / 64; ++ch) {
+                    uint32_t o[32];
+                    tmem_ld32(tO + ch * 32, o);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                tmem_st32(tO + ch * 32, o);
-              }
-            }
-          }
-          // pass 2: P = exp2(S - m), packed to 16 bits over the columns already consumed
-          float psum = 0.f;
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            if (hf >= nh) break;
-            uint32_t sr[64];
-            tmem_ld64(tS + hf * 64, sr);
-            tmem_wait_ld();
-            uint32_t pk[32];
-            if (full) {
-              float ps0 = 0.f, ps1 = 0.f;
-#pragma unroll
-              for (int c = 0; c < 64; c += 2) {
-                const float p0 = exp2f(__uint_as_float(sr[c]) - m_used);
-                const float p1 = exp2f(__uint_as_float(sr[c + 1]) - m_used);
-                ps0 += p0;
-                ps1 += p1;
-                pk[c >> 1] = pack2<T16>(p0, p1);
-              }
-              psum += ps0 + ps1;
-            } else {
-              // (a row with no valid column so far has m_used = -inf and selects 0 everywhere)
-              const int l2 = lo - hf * 64, h2 = hi - hf * 64;
-#pragma unroll
-              for (int c = 0; c < 64; c += 2) {
-                const float p0 = (c >= l2 && c <= h2) ? exp2f(__uint_as_float(sr[c]) - m_used) : 0.f;
-                const float p1 = (c + 1 >= l2 && c + 1 <= h2) ? exp2f(__uint_as_float(sr[c + 1]) - m_used) : 0.f;
-                psum += p0 + p1;
-                pk[c >> 1] = pack2<T16>(p0, p1);
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    tmem_st32(tO + ch * 32, o);
+                  }
+                }
               }
             }
-            tmem_st32(tS + hf * 32, pk);
+            // pass 2: P = exp2(S - m)
+            l_sum[x] += nh == 2 ? form_p(std::integral_constant<int, 64>{}, tS, full, lo, hi, m_used[x])
+                                : form_p(std::integral_constant<int, 32>{}, tS, full, lo, hi, m_used[x]);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars.p_ready[x]);
           }
-          l_sum += psum;
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(&bars.p_ready[x]);
         }
         if (!alive) break;
-        // ---- hand this k-tile's row statistics to the fold warpgroup
-        {
-          float* srow = stats + (((kt_count & 1) * 2 + x) * 128 + row) * 2;
-          srow[0] = m_used;
-          srow[1] = l_sum;
+        // ---- hand this k-tile's row statistics to the fold warpgroup: (reference, sum of warpgroup 0, of warpgroup 1)
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          float* srow = stats + (((kt_count & 1) * 2 + x) * 128 + row) * 4;
+          if (wg == 0) {
+            srow[0] = m_used[x];
+            srow[1] = l_sum[x];
+          } else {
+            srow[2] = l_sum[x];
+          }
+          mbar_arrive(&bars.stats_ready[x]);
         }
-        mbar_arrive(&bars.stats_ready[x]);
       }
       if (!alive) break;
     }
@@ -563,9 +602,9 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         for (int x = 0; x < 2; ++x) {
           alive = alive && __all_sync(0xffffffffu, mbar_wait(&bars.stats_ready[x], par, abort_flag));
           if (!alive) break;
-          const float* srow = stats + ((par * 2 + x) * 128 + row) * 2;
+          const float* srow = stats + ((par * 2 + x) * 128 + row) * 4;
           m_r[x] = srow[0];
-          l_r[x] = srow[1];
+          l_r[x] = srow[1] + srow[2];
           const int qx = x == 0 ? qa : qb;
           valid[x] = p.causal ? (k_r <= qx && qx - k_r <= p.k2w) : (k_r < T);
           float wm = valid[x] ? m_r[x] : -INFINITY;
