@@ -66,6 +66,38 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return mbar_wait_limit(bar, parity, abort_flag, kWaitTicks);
 }
 
+// ------------------------------------------------------------------ CTA pairs (thread-block clusters of two)
+// A pair of CTAs on the two SMs of one TPC can run tcgen05.mma with cta_group::2: one instruction, issued by the
+// even CTA, multiplies 256 rows (128 per CTA) with the B operand split along N between the two CTAs' shared
+// memories.  The helpers below are what the pair needs besides: rank, pair-wide barrier, arrival on a barrier of
+// the other CTA.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// (hardware barrier over all threads of the cluster: every thread of both CTAs must reach it)
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `bar` as seen in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mbar_in_cta(uint64_t* bar, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(bar)), "r"(rank));
+  return r;
+}
+// (default semantics, release at CTA scope, as for a local arrival: what is handed over lives in tensor memory or
+//  was published to the async proxy by the caller's fence; a cluster-scope release costs a memory barrier of
+//  several hundred cycles per arrival, measured as a doubled soft-max stage)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Bounded wait on a barrier of this CTA that, when PAIR, the other CTA of the pair may arrive on.
+template <bool PAIR>
+__device__ __forceinline__ bool mbar_wait_x(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait(bar, parity, abort_flag);
+}
+
 // ------------------------------------------------------------------ fences
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -80,6 +112,16 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"((uint64_t)m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+// The same load issued by a CTA of a pair, its bytes counted on a barrier of the pair's even CTA (`bar_cluster_addr`
+// from mbar_in_cta(bar, 0)); the destination is the issuing CTA's own shared memory.
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y,
+                                                 int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"((uint64_t)m), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 
@@ -108,6 +150,18 @@ __device__ __forceinline__ void tmem_relinquish() {
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// The same for a CTA pair (executed by the same warp of both CTAs).
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
 // ------------------------------------------------------------------ descriptors
@@ -186,6 +240,35 @@ __device__ __forceinline__ void mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accum)
       : "memory");
+}
+// CTA-pair forms (cta_group::2, issued by one thread of the even CTA; M counts the rows of both CTAs, each CTA
+// supplies its own A rows and its half of B's N extent at the same shared / tensor memory offsets).
+__device__ __forceinline__ void mma_ss_lo_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                               uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_lo_pair(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                               uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accum)
+      : "memory");
+}
+// Arrive on the barrier at `bar`'s offset in both CTAs of the pair once every MMA issued so far has finished.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"((uint16_t)3)
+               : "memory");
 }
 // Arrive on `bar` once every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {

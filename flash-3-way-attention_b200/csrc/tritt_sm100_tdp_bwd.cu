@@ -33,6 +33,9 @@
 // The fold warpgroup drains G / U of tile t (TMEM -> registers -> shared memory -> TMA reduce-add)
 // while the other warps already run tile t+1.  Work item = (query, head, role); it walks the row tiles
 // x <= q and, inside, the column slabs c <= q.
+// On request (TRITT_FLAG_BWD_CTA_PAIRS) the same kernel runs as clusters of two CTAs: each CTA keeps its own query,
+// operand tiles, soft-max and fold, the even CTA issues every product for both (cta_group::2, 256 rows), the column
+// tiles are split between the two shared memories, and hand-offs to the issuing thread cross the pair.
 #include "tritt_sm100_tdp.cuh"
 
 #include <type_traits>
@@ -103,12 +106,24 @@ __device__ __forceinline__ int prob_shift(int q, int causal, int T, int k1w, int
   return 0;
 }
 
-template <int D, typename T16, int NSW>
+// The four 64-row-box maps of the key / value tensors are used by the CTA-pair variant only.
+struct BwdHalfMaps {
+  CUtensorMap k1, k2, sv1, v2;
+};
+
+// PAIR: the kernel runs as clusters of two CTAs that take two queries of one (head, role) in lockstep: CTA `rank`
+// owns query 2 i + rank with its own operand tiles, soft-max and fold, and the even CTA issues every product for both
+// with cta_group::2 (M = 256: 128 pair rows per CTA).  The column tiles are then shared: each CTA holds half of a
+// tile's N extent per product (64 of its 128 rows for S / dP, 64 of its D columns for G / U), so the tensor cores
+// read 128 KB of shared memory per slab and SM instead of 192 KB.
+template <int D, typename T16, int NSW, bool PAIR>
 __global__ void __launch_bounds__(BwdThreads<NSW>::kTotal, 1)
 tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__ CUtensorMap tmK2,
                const __grid_constant__ CUtensorMap tmSV1, const __grid_constant__ CUtensorMap tmV2,
                const __grid_constant__ CUtensorMap tmDK1, const __grid_constant__ CUtensorMap tmDK2,
-               const __grid_constant__ CUtensorMap tmDSV1, const __grid_constant__ CUtensorMap tmDV2, BwdParams p) {
+               const __grid_constant__ CUtensorMap tmDSV1, const __grid_constant__ CUtensorMap tmDV2,
+               const __grid_constant__ BwdHalfMaps half, BwdParams p) {
+  static_assert(!PAIR || D == 128, "the CTA-pair tile layout is written for head dimension 128");
   using Cfg = BwdCfg<D>;
   constexpr int NS = Cfg::kStages;
   constexpr int KH = D / 64;
@@ -132,17 +147,20 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       mbar_init(&bars.ring_empty[i], 1);
     }
     mbar_init(&bars.xy_full, 1);
-    mbar_init(&bars.ax_ready, kNumSoftmax);
-    mbar_init(&bars.ay_ready, kNumSoftmax);
+    // (hand-offs to the issuing thread: every thread arrives, or, in a pair, one lane per warp of both CTAs on the
+    //  even CTA's barrier)
+    constexpr uint32_t kToMmaSm = PAIR ? 2 * kNumSoftmax / 32 : kNumSoftmax, kToMmaFold = PAIR ? 2 * 4 : 128;
+    mbar_init(&bars.ax_ready, kToMmaSm);
+    mbar_init(&bars.ay_ready, kToMmaSm);
     mbar_init(&bars.a_free, kNumSoftmax);
     mbar_init(&bars.s_ready, 1);
     mbar_init(&bars.dp_ready, 1);
-    mbar_init(&bars.p_ready[0], kNumSoftmax);
-    mbar_init(&bars.p_ready[1], kNumSoftmax);
-    mbar_init(&bars.ds_ready, kNumSoftmax);
+    mbar_init(&bars.p_ready[0], kToMmaSm);
+    mbar_init(&bars.p_ready[1], kToMmaSm);
+    mbar_init(&bars.ds_ready, kToMmaSm);
     mbar_init(&bars.gu_done, 1);
-    mbar_init(&bars.u_free, 128);
-    mbar_init(&bars.g_free, 128);
+    mbar_init(&bars.u_free, kToMmaFold);
+    mbar_init(&bars.g_free, kToMmaFold);
     mbar_init(&bars.sm_sync, kNumSoftmax);
     mbar_init(&bars.fold_sync, 128);
     mbar_init(&bars.vec_free[0], 128);
@@ -150,27 +168,56 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     fence_barrier_init();
   }
   if (warp == 0) {
-    tmem_alloc(&bars.tmem_base, 512);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(&bars.tmem_base, 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&bars.tmem_base, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the other CTA's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
   volatile int* abort_flag = &bars.abort_flag;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  // work is dealt to CTAs, or to CTA pairs
+  const long unit = PAIR ? (long)(blockIdx.x >> 1) : (long)blockIdx.x;
+  const long n_units = PAIR ? (long)(gridDim.x >> 1) : (long)gridDim.x;
+  // hand-off to the issuing thread (after the caller's fences)
+  auto to_mma = [&](uint64_t* bar) {
+    if constexpr (PAIR) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mbar_in_cta(bar, 0));
+    } else {
+      mbar_arrive(bar);
+    }
+  };
 
   const int T = p.T;
-  const long n_items = (long)p.nq * p.BN * 2;
+  // items: (query, head, role), or in a pair (two queries, head, role)
+  const long n_items = (long)(PAIR ? p.nq / 2 : p.nq) * p.BN * 2;
 
   // item -> (role, head, query); late (expensive) queries first.  Items 2r and 2r + 1 are the two roles of one (head,
   // query); which of them is which alternates with r in blocks of half the grid, so that the items of one CTA
   // (gridDim.x apart) alternate between the roles: role-0 tiles cost more (their fold also forms dQ), and a CTA
   // that only ever saw one role would finish 6 % later than its neighbour.
-  auto decode = [&](long item, int& role, int& bh, int& q) {
+  // In a pair `q` is this CTA's query and `qr` the later one of the two, whose tile ranges both CTAs walk (the
+  // earlier query masks what lies beyond it).
+  auto decode = [&](long item, int& role, int& bh, int& q, int& qr) {
     const long r = item >> 1;
-    role = (int)((item ^ (r / ((gridDim.x + 1) >> 1))) & 1);
+    role = (int)((item ^ (r / ((n_units + 1) >> 1))) & 1);
     bh = (int)(r % p.BN);
-    q = p.q_rem + (p.nq - 1 - (int)(r / p.BN)) * p.q_mod;
+    if constexpr (PAIR) {
+      const int i_hi = p.nq - 1 - 2 * (int)(r / p.BN);
+      q = p.q_rem + (i_hi - 1 + (int)rank) * p.q_mod;
+      qr = p.q_rem + i_hi * p.q_mod;
+    } else {
+      q = p.q_rem + (p.nq - 1 - (int)(r / p.BN)) * p.q_mod;
+      qr = q;
+    }
   };
   // Causal mask j <= q <= j + k1w, k <= q <= k + k2w, k - kkl <= j <= k + kkr, seen from a role's rows x and
   // columns c (role 0: x = k, c = j; role 1: x = j, c = k):  x in [q - xw, q],  c in [q - cw, q],  c in [x - below, x + above].
@@ -210,44 +257,58 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       for (int i = 0; i < 8; ++i) tma_prefetch_desc(maps[i]);
       uint32_t xt_count = 0, pos = 0;
       bool alive = true;
-      auto load_stage = [&](const CUtensorMap* tm, int row0, int bh) -> bool {
+      // One column tile (128 rows of Kc or Vc) into the next ring stage.  In a pair each CTA fetches what its half
+      // of the products reads: rows [64 rank, 64 rank + 64) of the tile (both 64-column halves, 8 KB each: the B
+      // operand of S / dP) and columns [64 rank, 64 rank + 64) of all 128 rows (16 KB: the B operand of G / U); the
+      // bytes of both CTAs are counted on the even CTA's barrier, where the issuing thread waits.
+      auto load_stage = [&](const CUtensorMap* tm, const CUtensorMap* tm_half, int row0, int bh) -> bool {
         const int st = pos % NS;
-        if (!mbar_wait(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag)) return false;
-        mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kTileA);
-        for (int hh = 0; hh < KH; ++hh)
-          tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kTileA + hh * 16384, tm, &bars.ring_full[st], hh * 64, row0, bh);
+        if (!mbar_wait_x<PAIR>(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag)) return false;
+        uint8_t* dst = smem + Cfg::kOffRing + st * Cfg::kTileA;
+        if constexpr (PAIR) {
+          if (rank == 0) mbar_arrive_expect_tx(&bars.ring_full[st], 2 * Cfg::kTileA);
+          const uint32_t full0 = mbar_in_cta(&bars.ring_full[st], 0);
+          tma_load_3d_pair(dst, tm_half, full0, 0, row0 + 64 * (int)rank, bh);
+          tma_load_3d_pair(dst + 8192, tm_half, full0, 64, row0 + 64 * (int)rank, bh);
+          tma_load_3d_pair(dst + 16384, tm, full0, 64 * (int)rank, row0, bh);
+        } else {
+          mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kTileA);
+          for (int hh = 0; hh < KH; ++hh) tma_load_3d(dst + hh * 16384, tm, &bars.ring_full[st], hh * 64, row0, bh);
+        }
         ++pos;
         return true;
       };
-      for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-        int role, bh, q, xt0, nxt;
-        decode(item, role, bh, q);
+      for (long item = unit; item < n_items && alive; item += n_units) {
+        int role, bh, q, qr, xt0, nxt;
+        decode(item, role, bh, q, qr);
         const Win win = role_win(role);
-        x_range(q, win, xt0, nxt);
+        x_range(qr, win, xt0, nxt);
         // role 0: columns K1 / SiLU(V1), rows K2 / V2;   role 1: columns K2 / V2, rows K1 / SiLU(V1)
         const CUtensorMap* tmKc = role == 0 ? &tmK1 : &tmK2;
         const CUtensorMap* tmVc = role == 0 ? &tmSV1 : &tmV2;
+        const CUtensorMap* tmKcH = role == 0 ? &half.k1 : &half.k2;
+        const CUtensorMap* tmVcH = role == 0 ? &half.sv1 : &half.v2;
         const CUtensorMap* tmX = role == 0 ? &tmK2 : &tmK1;
         const CUtensorMap* tmY = role == 0 ? &tmV2 : &tmSV1;
         for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
           int c0, ncs;
-          c_range(q, win, xt, c0, ncs);
+          c_range(qr, win, xt, c0, ncs);
           // the tile's first key / value slab does not depend on the operand buffers: fetch it before waiting for them
-          alive = load_stage(tmKc, c0 * kBC, bh);
-          if (alive) alive = load_stage(tmVc, c0 * kBC, bh);
-          if (!alive || !mbar_wait(&bars.a_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+          alive = load_stage(tmKc, tmKcH, c0 * kBC, bh);
+          if (alive) alive = load_stage(tmVc, tmVcH, c0 * kBC, bh);
+          if (!alive || !mbar_wait_x<PAIR>(&bars.a_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
           mbar_arrive_expect_tx(&bars.xy_full, 2 * Cfg::kTileA);
           for (int hh = 0; hh < KH; ++hh) {
             tma_load_3d(smem + Cfg::kOffA + hh * 16384, tmX, &bars.xy_full, hh * 64, xt * 128, bh);
             tma_load_3d(smem + Cfg::kOffA2 + hh * 16384, tmY, &bars.xy_full, hh * 64, xt * 128, bh);
           }
           for (int c = c0 + 1; c < c0 + ncs && alive; ++c) {
-            alive = load_stage(tmKc, c * kBC, bh);
-            if (alive) alive = load_stage(tmVc, c * kBC, bh);
+            alive = load_stage(tmKc, tmKcH, c * kBC, bh);
+            if (alive) alive = load_stage(tmVc, tmVcH, c * kBC, bh);
           }
         }
       }
-      if (!alive) {
+      if (!alive && (!PAIR || rank == 0)) {
         const uint32_t first = pos > (uint32_t)NS ? pos - NS : 0;
         for (uint32_t q2 = first; q2 < pos; ++q2) {
           const long long t0 = clock64();
@@ -258,20 +319,33 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       constexpr int kFmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t idesc_s = make_idesc_f16(128, kBC, kFmt, false, false);
-      constexpr uint32_t idesc_g = make_idesc_f16(128, D, kFmt, false, true);
+      constexpr int kM = PAIR ? 256 : 128;   // rows of one instruction (both CTAs of a pair)
+      constexpr uint32_t idesc_s = make_idesc_f16(kM, kBC, kFmt, false, false);
+      constexpr uint32_t idesc_g = make_idesc_f16(kM, D, kFmt, false, true);
       // descriptor low words; per instruction only a constant (in 16-byte units) is added
       constexpr uint32_t kHi = desc_hi(1024);
       constexpr uint32_t kTile16 = Cfg::kTileA >> 4;
       const uint32_t aLo = desc_lo(smem_u32(smem + Cfg::kOffA), 16), a2Lo = desc_lo(smem_u32(smem + Cfg::kOffA2), 16);
       const uint32_t ringK = desc_lo(smem_u32(smem + Cfg::kOffRing), 16);      // K-major view of a stage
-      const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing), 16384);  // row-major (MN-major) view
+      // row-major (MN-major) view; in a pair the stage's second half: this CTA's 64 columns of all 128 rows
+      const uint32_t ringMN = desc_lo(smem_u32(smem + Cfg::kOffRing + (PAIR ? 16384 : 0)), 16384);
+      // K-major view: 64-column blocks of a tile are 16 KB apart, of a pair's 64-row half 8 KB
+      constexpr uint32_t kBlkK = (PAIR ? 8192 : 16384) >> 4;
+      auto commit = [&](uint64_t* bar) {
+        if constexpr (PAIR) mma_commit_pair(bar); else mma_commit(bar);
+      };
+      auto mma_ss_any = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+        if constexpr (PAIR) mma_ss_lo_pair(d, a_lo, b_lo, kHi, idesc, acc); else mma_ss_lo(d, a_lo, b_lo, kHi, idesc, acc);
+      };
+      auto mma_ts_any = [&](uint32_t d, uint32_t a_t, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+        if constexpr (PAIR) mma_ts_lo_pair(d, a_t, b_lo, kHi, idesc, acc); else mma_ts_lo(d, a_t, b_lo, kHi, idesc, acc);
+      };
       uint32_t xt_count = 0, base = 0, n = 0;
       bool alive = true;
       auto wait_full = [&](uint32_t pos) {
-        return mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
+        return mbar_wait_x<PAIR>(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
       };
       // One 8-instruction accumulation chain each (D = 128): S = A Kc^T, dP = A' Vc^T (operands in shared
       // memory, key/value tile K-major), U (+)= P Vc, G (+)= dS Kc (P / dS from tensor memory, the tile row-major).
@@ -280,10 +354,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         const uint32_t bLo = ringK + (pos % NS) * kTile16;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-          mma_ss_lo(tmem + Cfg::kTmemS, aLo + kk, bLo + kk, kHi, idesc_s, k > 0);
+          const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2, kb = (k >> 2) * kBlkK + (k & 3) * 2;
+          mma_ss_any(tmem + Cfg::kTmemS, aLo + kk, bLo + kb, idesc_s, k > 0);
         }
-        mma_commit(&bars.s_ready);
+        commit(&bars.s_ready);
         return true;
       };
       auto issue_dp = [&](uint32_t pos) -> bool {
@@ -291,10 +365,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         const uint32_t bLo = ringK + (pos % NS) * kTile16;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-          mma_ss_lo(tmem + Cfg::kTmemDP, a2Lo + kk, bLo + kk, kHi, idesc_s, k > 0);
+          const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2, kb = (k >> 2) * kBlkK + (k & 3) * 2;
+          mma_ss_any(tmem + Cfg::kTmemDP, a2Lo + kk, bLo + kb, idesc_s, k > 0);
         }
-        mma_commit(&bars.dp_ready);
+        commit(&bars.dp_ready);
         return true;
       };
       // soft-max warpgroup g packed its CW columns of P into S[CW*g, CW*g + CW/2) and of dS into dP[CW*g, ...)
@@ -308,59 +382,59 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         for (int k = 0; k < kBC / 16; ++k) {
           if (((k % KPW) >= KPW / 2) != (half == 1)) continue;
           const uint32_t a = tmem + Cfg::kTmemS + (k / KPW) * CW + (k % KPW) * 8;
-          mma_ts_lo(tmem + Cfg::kTmemU, a, ringMN + st * kTile16 + k * (2048 >> 4), kHi, idesc_g, first ? acc : 1u);
+          mma_ts_any(tmem + Cfg::kTmemU, a, ringMN + st * kTile16 + k * (2048 >> 4), idesc_g, first ? acc : 1u);
           first = false;
         }
-        if (half == 1) mma_commit(&bars.ring_empty[st]);
+        if (half == 1) commit(&bars.ring_empty[st]);
       };
       auto issue_g = [&](uint32_t pos, uint32_t acc) {
         const uint32_t st = pos % NS;
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
           const uint32_t a = tmem + Cfg::kTmemDP + (k / KPW) * CW + (k % KPW) * 8;
-          mma_ts_lo(tmem + Cfg::kTmemG, a, ringMN + st * kTile16 + k * (2048 >> 4), kHi, idesc_g, k > 0 ? 1u : acc);
+          mma_ts_any(tmem + Cfg::kTmemG, a, ringMN + st * kTile16 + k * (2048 >> 4), idesc_g, k > 0 ? 1u : acc);
         }
-        mma_commit(&bars.ring_empty[st]);
+        commit(&bars.ring_empty[st]);
       };
 
-      for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-        int role, bh, q, xt0, nxt;
-        decode(item, role, bh, q);
+      for (long item = unit; item < n_items && alive; item += n_units) {
+        int role, bh, q, qr, xt0, nxt;
+        decode(item, role, bh, q, qr);
         const Win win = role_win(role);
-        x_range(q, win, xt0, nxt);
+        x_range(qr, win, xt0, nxt);
         for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
           int c0, ncs;
-          c_range(q, win, xt, c0, ncs);
+          c_range(qr, win, xt, c0, ncs);
           // the first score product starts while the soft-max warps still form the dP operand
-          if (!mbar_wait(&bars.ax_ready, xt_count & 1, abort_flag)) { alive = false; break; }
+          if (!mbar_wait_x<PAIR>(&bars.ax_ready, xt_count & 1, abort_flag)) { alive = false; break; }
           tc_fence_after();
           if (!issue_s(base)) { alive = false; break; }
-          if (!mbar_wait(&bars.ay_ready, xt_count & 1, abort_flag)) { alive = false; break; }
+          if (!mbar_wait_x<PAIR>(&bars.ay_ready, xt_count & 1, abort_flag)) { alive = false; break; }
           tc_fence_after();
           if (!issue_dp(base + 1)) { alive = false; break; }
           for (int c = 0; c < ncs && alive; ++c, ++n) {
             const bool more = c + 1 < ncs;
-            if (!mbar_wait(&bars.p_ready[0], n & 1, abort_flag)) { alive = false; break; }
+            if (!mbar_wait_x<PAIR>(&bars.p_ready[0], n & 1, abort_flag)) { alive = false; break; }
             if (c == 0) {
               // the fold warpgroup must have drained the previous tile's U
-              if (!mbar_wait(&bars.u_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+              if (!mbar_wait_x<PAIR>(&bars.u_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
             }
             tc_fence_after();
             issue_u_half(base + 2 * c + 1, c > 0, 0);
-            if (!mbar_wait(&bars.p_ready[1], n & 1, abort_flag)) { alive = false; break; }
+            if (!mbar_wait_x<PAIR>(&bars.p_ready[1], n & 1, abort_flag)) { alive = false; break; }
             tc_fence_after();
             issue_u_half(base + 2 * c + 1, c > 0, 1);
             if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
-            if (!mbar_wait(&bars.ds_ready, n & 1, abort_flag)) { alive = false; break; }
+            if (!mbar_wait_x<PAIR>(&bars.ds_ready, n & 1, abort_flag)) { alive = false; break; }
             if (c == 0) {
               // ... and the previous tile's G
-              if (!mbar_wait(&bars.g_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+              if (!mbar_wait_x<PAIR>(&bars.g_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
             }
             tc_fence_after();
             issue_g(base + 2 * c, c > 0);
             if (more && !issue_dp(base + 2 * (c + 1) + 1)) { alive = false; break; }
           }
-          if (alive) mma_commit(&bars.gu_done);
+          if (alive) commit(&bars.gu_done);
           base += 2 * ncs;
         }
       }
@@ -377,23 +451,23 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     bool alive = true;
     auto sm_sync = [&]() -> bool {
       mbar_arrive(&bars.sm_sync);
-      const bool ok = mbar_wait(&bars.sm_sync, sync_phase & 1, abort_flag);
+      const bool ok = mbar_wait_x<PAIR>(&bars.sm_sync, sync_phase & 1, abort_flag);
       ++sync_phase;
       return __all_sync(0xffffffffu, ok);
     };
 
-    for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++item_count) {
-      int role, bh, q, xt0, nxt;
-      decode(item, role, bh, q);
+    for (long item = unit; item < n_items && alive; item += n_units, ++item_count) {
+      int role, bh, q, qr, xt0, nxt;
+      decode(item, role, bh, q, qr);
       const Win win = role_win(role);
-      x_range(q, win, xt0, nxt);
+      x_range(qr, win, xt0, nxt);
       const size_t hb = (size_t)bh * T * D;
       float* qv = vec + (item_count & 1) * 2 * D;  // Q[q, :] (double-buffered by item: the fold warpgroup of the
       float* dov = qv + D;                         // dO[q, :]  previous item may still be reading its copy)
       if (!sm_sync()) { alive = false; break; }    // previous item's readers of misc are done
       // the fold warpgroup can lag two items behind: wait until it has stopped reading this copy of the vectors
       alive = __all_sync(0xffffffffu,
-                         mbar_wait(&bars.vec_free[item_count & 1], ((item_count >> 1) & 1) ^ 1, abort_flag));
+                         mbar_wait_x<PAIR>(&bars.vec_free[item_count & 1], ((item_count >> 1) & 1) ^ 1, abort_flag));
       if (!alive) break;
       const float scale2 = p.alpha * kLog2e;
       if (wg == 0) {
@@ -417,9 +491,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 
       for (int xt = xt0; xt < xt0 + nxt && alive; ++xt, ++xt_count) {
         int c0, ncs;
-        c_range(q, win, xt, c0, ncs);
+        c_range(qr, win, xt, c0, ncs);
         // ---- operand formation (in place): A = scale2*Q[q] (.) X tile,  A' = dO[q] (.) Y tile
-        alive = __all_sync(0xffffffffu, mbar_wait(&bars.xy_full, xt_count & 1, abort_flag));
+        alive = __all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.xy_full, xt_count & 1, abort_flag));
         if (!alive) break;
         // (each warpgroup takes half of the columns; the eight Q / dO values of a 16-byte chunk are the same for all rows)
 #pragma unroll
@@ -439,7 +513,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           *reinterpret_cast<uint4*>(smem + Cfg::kOffA + off) = make_uint4(wx[0], wx[1], wx[2], wx[3]);
         }
         fence_async_smem();
-        mbar_arrive(&bars.ax_ready);
+        to_mma(&bars.ax_ready);
 #pragma unroll
         for (int ci = 0; ci < D / 8 / NSW; ++ci) {
           const int cc = wg * (D / 8 / NSW) + ci;
@@ -457,7 +531,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           *reinterpret_cast<uint4*>(smem + Cfg::kOffA2 + off) = make_uint4(wy[0], wy[1], wy[2], wy[3]);
         }
         fence_async_smem();
-        mbar_arrive(&bars.ay_ready);
+        to_mma(&bars.ay_ready);
 
         // columns this row sees: [c_lo, c_hi] (empty for a row outside its own range: its P is zero)
         const int x_r = xt * 128 + row;
@@ -474,7 +548,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           const int lo = c_lo - (c0 + c) * kBC - wg * CW, hi = c_hi - (c0 + c) * kBC - wg * CW;
           uint32_t pk[CW / 2];
           // ---- S -> P
-          alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready, n & 1, abort_flag));
+          alive = __all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.s_ready, n & 1, abort_flag));
           if (!alive) break;
           tc_fence_after();
           static_assert(CW == 64, "the two-half hand-off of P is written for two soft-max warpgroups");
@@ -507,10 +581,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             tmem_st16(tS + hf * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[hf * 16]));
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars.p_ready[hf]);
+            to_mma(&bars.p_ready[hf]);
           }
           // ---- dP, P -> dS
-          alive = __all_sync(0xffffffffu, mbar_wait(&bars.dp_ready, n & 1, abort_flag));
+          alive = __all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.dp_ready, n & 1, abort_flag));
           if (!alive) break;
           tc_fence_after();
           if (c == ncs - 1) {
@@ -533,7 +607,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           tmem_st(tDP, dk);  // dS -> first half of this warpgroup's dP columns
           tmem_wait_st();
           tc_fence_before();
-          mbar_arrive(&bars.ds_ready);
+          to_mma(&bars.ds_ready);
         }
         if (!alive) break;
       }
@@ -552,15 +626,15 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     bool alive = true;
     auto fold_sync = [&]() -> bool {
       mbar_arrive(&bars.fold_sync);
-      const bool ok = mbar_wait(&bars.fold_sync, sync_phase & 1, abort_flag);
+      const bool ok = mbar_wait_x<PAIR>(&bars.fold_sync, sync_phase & 1, abort_flag);
       ++sync_phase;
       return __all_sync(0xffffffffu, ok);
     };
-    for (long item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++item_count) {
-      int role, bh, q, xt0, nxt;
-      decode(item, role, bh, q);
+    for (long item = unit; item < n_items && alive; item += n_units, ++item_count) {
+      int role, bh, q, qr, xt0, nxt;
+      decode(item, role, bh, q, qr);
       const Win win = role_win(role);
-      x_range(q, win, xt0, nxt);
+      x_range(qr, win, xt0, nxt);
       const size_t hb = (size_t)bh * T * D;
       const T16* Xg = (const T16*)p.x[role] + hb;
       const CUtensorMap* tmDX = role == 0 ? &tmDK2 : &tmDK1;
@@ -583,7 +657,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         const bool x_ok = (p.causal ? (x_r <= q && q - x_r <= win.xw) : true) && x_r < T;
         // (rows outside the query's range carry zeros: a warp whose 32 rows all are has nothing to add)
         const bool warp_rows_live = __any_sync(0xffffffffu, x_ok);
-        alive = __all_sync(0xffffffffu, mbar_wait(&bars.gu_done, xt_count & 1, abort_flag));
+        alive = __all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.gu_done, xt_count & 1, abort_flag));
         if (!alive) break;
         tc_fence_after();
 #pragma unroll 1
@@ -626,12 +700,12 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           if (pc == D / 32 - 1) {
             // last piece of U is in registers: that accumulator may be overwritten
             tc_fence_before();
-            mbar_arrive(&bars.u_free);
+            to_mma(&bars.u_free);
           }
           if (pc == 2 * (D / 32) - 1) {
             // likewise G
             tc_fence_before();
-            mbar_arrive(&bars.g_free);
+            to_mma(&bars.g_free);
             if (xt == xt0 + nxt - 1) mbar_arrive(&bars.vec_free[item_count & 1]);  // and this query's vectors are done with
           }
           uint8_t* slot = slots + (round & 1) * 4096;
@@ -681,7 +755,10 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
+  if constexpr (PAIR) cluster_sync_all();  // neither CTA frees tensor memory or leaves while the other may still use it
+  if (warp == 0) {
+    if constexpr (PAIR) tmem_dealloc_pair(tmem, 512); else tmem_dealloc(tmem, 512);
+  }
   if (tid == 0 && bars.abort_flag && p.status) atomicOr(p.status, 4);
 }
 
@@ -718,12 +795,50 @@ int launch_bwd(const TdpArgs& a) {
   p.kkr = a.mask.kkr;
   p.alpha = a.alpha;
   p.status = a.status_word;
-  if (p.nq > 0) {
-    auto kern = tdp_bwd_kernel<D, T16, NSW>;
+  BwdHalfMaps half{};
+  // CTA pairs (on request: TRITT_FLAG_BWD_CTA_PAIRS): head dimension 128, an even number of queries, and a mask
+  // whose tile ranges are the same for two neighbouring queries (no windows); everything else runs one CTA per item.
+  const TdpMask& m = a.mask;
+  bool pair = (a.flags & TRITT_FLAG_BWD_CTA_PAIRS) && D == 128 && p.nq >= 2 && p.nq % 2 == 0 &&
+              (!m.causal || (m.k1w >= a.T && m.k2w >= a.T && m.kkl >= a.T && m.kkr >= a.T));
+  if (p.nq > 0 && pair) {
+    if constexpr (D == 128) {
+      auto kern = tdp_bwd_kernel<D, T16, NSW, true>;
+      TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+      cudaLaunchConfig_t cfg{};
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.gridDim = dim3(2, 1, 1);
+      cfg.blockDim = dim3(BwdThreads<NSW>::kTotal, 1, 1);
+      cfg.dynamicSmemBytes = Cfg::kSmem;
+      cfg.stream = a.stream;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters < 1) {
+        (void)cudaGetLastError();
+        pair = false;   // no room for a pair on this device: one CTA per item
+      } else {
+        if ((rc = make_tmap_3d(&half.k1, a.k1, 2, D, a.T, BN, 64, 64))) return rc;
+        if ((rc = make_tmap_3d(&half.k2, a.k2, 2, D, a.T, BN, 64, 64))) return rc;
+        if ((rc = make_tmap_3d(&half.sv1, sv1, 2, D, a.T, BN, 64, 64))) return rc;
+        if ((rc = make_tmap_3d(&half.v2, a.v2, 2, D, a.T, BN, 64, 64))) return rc;
+        const long items = (long)(p.nq / 2) * BN * 2;
+        cfg.gridDim = dim3((unsigned)(2 * (items < clusters ? items : clusters)), 1, 1);
+        TRITT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tmK1, tmK2, tmSV1, tmV2, tmDK1, tmDK2, tmDSV1, tmDV2, half, p));
+        count_launch();
+      }
+    }
+  }
+  if (p.nq > 0 && !pair) {
+    auto kern = tdp_bwd_kernel<D, T16, NSW, false>;
     TRITT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     const long items = (long)p.nq * BN * 2;
     const int grid = (int)(items < num_sms() ? items : num_sms());
-    kern<<<grid, BwdThreads<NSW>::kTotal, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmDK1, tmDK2, tmDSV1, tmDV2, p);
+    kern<<<grid, BwdThreads<NSW>::kTotal, Cfg::kSmem, a.stream>>>(tmK1, tmK2, tmSV1, tmV2, tmDK1, tmDK2, tmDSV1, tmDV2, half, p);
     count_launch();
     TRITT_CUDA_OK(cudaGetLastError());
   }

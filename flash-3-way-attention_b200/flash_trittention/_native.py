@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libtritt_sm100.so")
 
 F32, F16, BF16 = 0, 1, 2
 OP_TDP_FWD, OP_TDP_BWD, OP_DPS_FWD, OP_DPS_BWD = 0, 1, 2, 3
-FLAG_FORCE_SIMT, FLAG_BWD_PARTIAL, FLAG_WIDE_OPERANDS = 1, 2, 4
+FLAG_FORCE_SIMT, FLAG_BWD_PARTIAL, FLAG_WIDE_OPERANDS, FLAG_BWD_CTA_PAIRS = 1, 2, 4, 8
 PATH_SIMT, PATH_TCGEN05 = 0, 1
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}

@@ -50,12 +50,17 @@ enum {
   TRITT_FLAG_BWD_PARTIAL = 2, /* tritt_tdp_bwd: leave the fp32 key-side partial sums in the workspace and do not
                                  write dk1/dk2/dv1/dv2 (the caller reduces them across ranks, then calls
                                  tritt_tdp_bwd_finalize) */
-  TRITT_FLAG_WIDE_OPERANDS = 4 /* triple-dot-product, bf16 inputs: form the operands with 11 significant bits (fp16
+  TRITT_FLAG_WIDE_OPERANDS = 4, /* triple-dot-product, bf16 inputs: form the operands with 11 significant bits (fp16
                                  copies) instead of bf16's 8, what the reference's `convert_to_float32` asks of its TF32
                                  dot products.  fp32 inputs always take that path on the tensor cores (head dimension
                                  64 / 128); fp16 inputs already have it.  Needs the larger workspace that
                                  tritt_workspace_bytes_flags() reports; an input element beyond fp16's range (65504)
                                  sets status bit 64. */
+  TRITT_FLAG_BWD_CTA_PAIRS = 8  /* tritt_tdp_bwd, 16-bit inputs, head dimension 128, no windows, an even number of
+                                 queries: run the backward kernel as clusters of two CTAs that share every key / value
+                                 tile (tcgen05 cta_group::2, 256-row products).  Same results up to the order of the
+                                 fp32 reduce-adds; measured 0.4 % slower per step than one CTA per item on a B200, so
+                                 it is not the default.  Ignored where it does not apply. */
 };
 
 /* kernel families, as reported by tritt_tdp_path() */

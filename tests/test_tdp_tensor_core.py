@@ -130,6 +130,30 @@ def test_backward_reference_test_distribution(dtype, D, causal):
     _bwd_case(1, 2, 160 if causal else 96, D, dtype, causal, 1.0, 1 / 8, seed=19 + D)
 
 
+@pytest.mark.parametrize("dtype,causal,T", [(torch.bfloat16, True, 384), (torch.float16, True, 200),
+                                            (torch.bfloat16, False, 192)])
+def test_backward_on_cta_pairs_matches_oracle_and_default_path(dtype, causal, T):
+    """TRITT_FLAG_BWD_CTA_PAIRS: the backward kernel as clusters of two CTAs (cta_group::2 products over two queries
+    that share every key / value tile).  Checked against the oracle with the usual bounds, and against the default
+    one-CTA-per-item launch, from which it may differ only by the order of the fp32 reduce-adds."""
+    B, N, D, alpha = 1, 3, 128, 1 / 128
+    q, k1, k2, v1, v2, dz = orc.make_inputs(B, N, T, D, scale=0.5, seed=31 + T, dtype=dtype)
+    t = [x.to(DEV) for x in (q, k1, k2, v1, v2)]
+    do = dz.to(DEV)
+    o, lse = torch.empty_like(t[0]), torch.empty(B, N, T, device=DEV)
+    _native.tdp_fwd(*t, o, lse, alpha, causal, None, None, None, None)
+    base = [torch.empty_like(t[0]) for _ in range(5)]
+    _native.tdp_bwd(*t, o, do, lse, *base, alpha, causal, None, None, None, None)
+    pair = [torch.full_like(t[0], float("nan")) for _ in range(5)]
+    _native.tdp_bwd(*t, o, do, lse, *pair, alpha, causal, None, None, None, None, flags=_native.FLAG_BWD_CTA_PAIRS)
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0
+    ref = orc.tdp_backward(q.float(), k1.float(), k2.float(), v1.float(), v2.float(), dz.float(), alpha, causal)
+    for name, got, want, same in zip(("dq", "dk1", "dk2", "dv1", "dv2"), pair, ref, base):
+        assert_close(name + " (pairs)", got, want, dtype)
+        assert_close(name + " (pairs vs default launch)", got, same, torch.float32, scale=100.0)
+
+
 def test_backward_query_shards_sum_to_full_gradient():
     """Query-sharded backward: each shard writes its rows of dq and leaves fp32 partial key-side sums;
     their sum, finalised once, equals the unsharded gradients (the multi-device path does the sum with
