@@ -18,10 +18,12 @@
 //                acc_x += P_x*SiLU(V1) with P_x read from TMEM (it overlays S_x) and the value tile used
 //                row-major (MN-major descriptor).  128-column slabs keep every accumulation chain at
 //                8 instructions of 128x128x16, the shape the pipe runs at full rate.
-//   warps 4-11   two soft-max warpgroups that work on the same slab, tile a then tile b, 64 of its 128 columns
-//                each (one row per thread): exp2 against the row's score bound, or, where that is too large,
-//                row max (exchanged between the two warps that share the rows) and lazy rescaling; P written
-//                back to TMEM as 16-bit over the first half of the columns just read; they also form A_a, A_b
+//   warps 4-11   two soft-max warpgroups (one row per thread); they also form A_a, A_b.  Where a head-wide bound on
+//                the scores is small (per-head statistics from a small kernel before this one) every row takes its
+//                own score bound as the soft-max reference and the warpgroups work on the same slab, tile a then
+//                tile b, 64 of its 128 columns each: one pass, exp2, P written back to TMEM as 16-bit over the
+//                first half of the columns just read.  Otherwise warpgroup x owns tile x and a thread its whole
+//                row: row maximum, exp2 with lazy rescaling of the accumulator, P over the first 64 columns of S_x
 //   warps 12-15  fold warpgroup: when a k-tile is finished, folds acc_x (times V2, soft-max over k) into
 //                the queries' running (max, sum, output) while the other warps start the next k-tile
 // Causal structure: for a fixed query the mask is "j <= q" on columns and "k <= q" on rows, so
@@ -51,8 +53,7 @@ template <int D> struct FwdCfg {
   static constexpr int kOffRed = kOffStats + 2 * 2 * 128 * 4 * 4;  // [2 tiles][4 warps][D] fp32 column sums
   static constexpr int kOffFstat = kOffRed + 2 * 4 * D * 4;        // [2 tiles][8] fp32 warp max / sum
   static constexpr int kOffNorm = kOffFstat + 2 * 8 * 4;            // [2 tiles][2 column halves][128] fp32: partial |A_row|^2
-  static constexpr int kOffXchg = kOffNorm + 2 * 2 * 128 * 4;       // [2 slots][2 warpgroups][128] fp32: row maxima being exchanged
-  static constexpr int kOffBars = kOffXchg + 2 * 2 * 128 * 4;
+  static constexpr int kOffBars = kOffNorm + 2 * 2 * 128 * 4;
   static constexpr int kSmem = kOffBars + 256;
   static constexpr int kTmemO = 256;  // S_a | S_b | acc_a | acc_b
 };
@@ -65,6 +66,8 @@ struct FwdParams {
   int k1w, k2w, kkl, kkr;  // windows of the causal mask (T or more = unbounded)
   float scale2;  // alpha * log2(e)
   const float* k1_norm2_max;  // [BN] largest squared row norm of K1 per head, or null (no score bound available)
+  const float* q_norm2_max;   // [BN] largest squared row norm of Q per head (with k1_norm2_max)
+  const float* k2_elem2_max;  // [BN] largest squared element of K2 per head (with k1_norm2_max)
   float bound_limit;          // rows whose score bound is below this skip the row-maximum pass
   int* status;
 };
@@ -75,7 +78,6 @@ struct FwdBarriers {
   uint64_t s_ready[2], p_ready[2];               // per tile, one phase per slab
   uint64_t o_done, o_free[2], stats_ready[2];    // per k-tile hand-offs with the fold warpgroup
   uint64_t fold_sync;
-  uint64_t xchg[4];                              // the two soft-max warps of a lane quadrant, per exchange of row maxima
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -112,7 +114,6 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       mbar_init(&bars.o_free[x], 128);
       mbar_init(&bars.stats_ready[x], 256);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(&bars.xchg[i], 64);
     mbar_init(&bars.o_done, 1);
     mbar_init(&bars.fold_sync, 128);
     fence_barrier_init();
@@ -177,6 +178,17 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     }
   };
   auto halves = [](int ja, int jb, int j0) { return jb < j0 + 64 ? 1 : (ja >= j0 + 64 ? 2 : 0); };
+  // How the soft-max warps divide a head's work.  Every score of the head is bounded by
+  // |s| max_q |Q_q| max |K2 element| max_j |K1_j|  (|A_row|^2 = s^2 sum_h Q_h^2 K2_h^2 <= s^2 max_h K2_h^2 |Q_q|^2).
+  // Where that is below the limit, every row can take its own score bound as soft-max reference (one pass, nothing
+  // to agree on between threads) and the two warpgroups split every slab's columns; otherwise each warpgroup owns one
+  // tile and a thread its whole row (maximum pass, rescaling).  Uniform over a work item, read by every role.
+  auto head_split = [&](int bh) -> bool {
+    if (!p.k1_norm2_max) return false;
+    const float b = fabsf(p.scale2) * sqrtf(__ldg(p.q_norm2_max + bh)) * sqrtf(__ldg(p.k2_elem2_max + bh)) *
+                    sqrtf(__ldg(p.k1_norm2_max + bh));
+    return b <= p.bound_limit;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -266,20 +278,20 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       };
       // acc_x (+)= P_x * SiLU(V1)tile  (one chain of 8 instructions; P_x overlays the first 64 columns of S_x);
       // hm != 0: P_x has 64 columns (4 instructions) and meets the lower or upper 64 rows of the value tile
-      auto issue_pv = [&](int x, uint32_t pos, uint32_t acc, int hm) {
+      // (split: P of a warpgroup's columns sits over the first half of them; otherwise over the first 64 columns of S_x)
+      auto issue_pv = [&](int x, uint32_t pos, uint32_t acc, int hm, bool split) {
         const uint32_t bLo = ringMN + (pos % NS) * kTile16;
         if (hm == 0) {
-          // (P of the slab's column half h sits in the first 32 columns of that half of S_x)
 #pragma unroll
           for (int k = 0; k < kBJ / 16; ++k)
-            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (k >> 2) * 64 + (k & 3) * 8, bLo + k * (2048 >> 4), kHi,
-                      idesc_pv, k > 0 ? 1u : acc);
+            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (split ? (k >> 2) * 64 + (k & 3) * 8 : k * 8),
+                      bLo + k * (2048 >> 4), kHi, idesc_pv, k > 0 ? 1u : acc);
         } else {
           const uint32_t bRow = bLo + (hm == 2 ? (4 * 2048) >> 4 : 0);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (k >> 1) * 32 + (k & 1) * 8, bRow + k * (2048 >> 4), kHi,
-                      idesc_pv, k > 0 ? 1u : acc);
+            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (split ? (k >> 1) * 32 + (k & 1) * 8 : k * 8),
+                      bRow + k * (2048 >> 4), kHi, idesc_pv, k > 0 ? 1u : acc);
         }
       };
 
@@ -287,6 +299,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         int bh, qa, qb, kt0, nkt;
         decode(item, bh, qa, qb);
         k_range(qa, qb, kt0, nkt);
+        const bool split = head_split(bh);
         for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
           int jt0, njt;
           j_range(qa, qb, kt, jt0, njt);
@@ -311,7 +324,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
               }
               tc_fence_after();
               if (x == 0 && !wait_full(pv)) { alive = false; break; }
-              issue_pv(x, pv, jt > 0, hm);
+              issue_pv(x, pv, jt > 0, hm, split);
               if (x == 1) release(pv);
               if (more) {
                 if (x == 0 && !wait_full(pk)) { alive = false; break; }
@@ -338,8 +351,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     float* stats = (float*)(smem + Cfg::kOffStats);
     float* norms = (float*)(smem + Cfg::kOffNorm);
-    float* xchg = (float*)(smem + Cfg::kOffXchg);
-    uint32_t kt_count = 0, n = 0, xphase = 0;
+    uint32_t kt_count = 0, n = 0;
     bool alive = true;
 
     // largest score of this thread's NC columns at TMEM address tS ([lo, hi]: the columns the row may see)
@@ -369,7 +381,8 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       return mx;
     };
     // P = exp2(S - m) of this thread's NC columns, packed to 16 bits over the first NC / 2 of them; returns their sum
-    auto form_p = [&](auto nc, uint32_t tS, bool full, int lo, int hi, float m) -> float {
+    // (written at tP, which lies within columns this thread has read)
+    auto form_p = [&](auto nc, uint32_t tS, uint32_t tP, bool full, int lo, int hi, float m) -> float {
       constexpr int NC = decltype(nc)::value;
       uint32_t sr[NC];
       if constexpr (NC == 64) tmem_ld64(tS, sr); else tmem_ld32(tS, sr);
@@ -404,7 +417,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           pk[c >> 1] = pack2<T16>(p0, p1);
         }
       }
-      tmem_st(tS, pk);
+      tmem_st(tP, pk);
       return ps0 + ps1;
     };
 
@@ -415,6 +428,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       const T16* Qg = (const T16*)p.q + (size_t)bh * T * D;
       // largest K1 row norm of this head: with |A_row| it bounds every score of the row (Cauchy-Schwarz)
       const float k1_max = p.k1_norm2_max ? sqrtf(__ldg(p.k1_norm2_max + bh)) : INFINITY;
+      const bool split = head_split(bh);
 
       for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
         int jt0, njt, ja, jb;
@@ -475,64 +489,101 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         fence_async_smem();   // generic-proxy stores above -> visible to the tensor core's reads
         mbar_arrive(&bars.a_ready);
 
-        // ---- walk over the slabs
-        float m_used[2] = {-INFINITY, -INFINITY}, l_sum[2] = {0.f, 0.f};
-        bool fast[2] = {false, false};
-        for (int jt = 0; jt < njt && alive; ++jt, ++n) {
-          // A slab with attended columns in one 64-column half only was computed for that half alone: its scores
-          // are in the first 64 columns of S_x and stand for the slab's columns [coff, coff + 64).
-          const int hm = halves(ja, jb, (jt0 + jt) * kBJ);
-          const int nh = hm ? 1 : 2, coff = hm == 2 ? 64 : 0;
-          const int cw = 32 * nh;                                  // columns of this warpgroup in this slab
-          const int j0 = (jt0 + jt) * kBJ + coff + wg * cw;      // its first column
+        if (split) {
+          // ---- walk over the slabs, both warpgroups on the same slab: tile a, then tile b; warpgroup `wg` takes the
+          // slab's columns [wg * 64, wg * 64 + 64) (32 of a half-width slab's 64).  The reference of every row is its
+          // score bound |A_row| * max_j |K1_j| (log2 units), which the head-wide bound keeps below the limit: P stays
+          // within [2^-2b, 1], representable in the 16-bit type, and no row maximum is needed.
+          float ref[2], l_sum[2] = {0.f, 0.f};
+#pragma unroll
+          for (int x = 0; x < 2; ++x) ref[x] = 0.f;
+          for (int jt = 0; jt < njt && alive; ++jt, ++n) {
+            // A slab with attended columns in one 64-column half only was computed for that half alone: its scores
+            // are in the first 64 columns of S_x and stand for the slab's columns [coff, coff + 64).
+            const int hm = halves(ja, jb, (jt0 + jt) * kBJ);
+            const int nh = hm ? 1 : 2, coff = hm == 2 ? 64 : 0;
+            const int cw = 32 * nh;                                  // columns of this warpgroup in this slab
+            const int j0 = (jt0 + jt) * kBJ + coff + wg * cw;      // its first column
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+              alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x], n & 1, abort_flag));
+              if (!alive) break;
+              tc_fence_after();
+              if (jt == 0) ref[x] = sqrtf(norms[(x * 2 + 0) * 128 + row] + norms[(x * 2 + 1) * 128 + row]) * k1_max;
+              // the last score product of this k-tile has read A_a and A_b
+              if (x == 1 && jt == njt - 1) mbar_arrive(&bars.a_free);
+              const uint32_t tS = tmem + lane_base + x * kBJ + wg * cw;
+              // this row's valid columns among the warpgroup's: [lo, hi]; the warp takes the unmasked code when all
+              // its rows see all of them
+              const int lo = c_lo[x] - j0, hi = c_hi[x] - j0;
+              const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= cw - 1);
+              // P over the first half of the columns this thread has read
+              l_sum[x] += nh == 2 ? form_p(std::integral_constant<int, 64>{}, tS, tS, full, lo, hi, ref[x])
+                                  : form_p(std::integral_constant<int, 32>{}, tS, tS, full, lo, hi, ref[x]);
+              tmem_wait_st();
+              tc_fence_before();
+              mbar_arrive(&bars.p_ready[x]);
+            }
+          }
+          if (!alive) break;
+          // ---- hand this k-tile's row statistics to the fold warpgroup: (reference, sum of warpgroup 0, of warpgroup 1)
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
+            float* srow = stats + (((kt_count & 1) * 2 + x) * 128 + row) * 4;
+            if (wg == 0) {
+              srow[0] = ref[x];
+              srow[1] = l_sum[x];
+            } else {
+              srow[2] = l_sum[x];
+            }
+            mbar_arrive(&bars.stats_ready[x]);
+          }
+        } else {
+          // ---- walk over the slabs, one warpgroup per tile (warpgroup 0: tile a), one whole row per thread: row
+          // maximum, exp2 with lazy rescaling of the accumulator.  A warp whose rows all have a score bound below the
+          // limit still uses the bound as reference and skips the maximum pass.  (Arrivals count twice: the barriers
+          // expect both warpgroups.)
+          const int x = wg;
+          const int c_lo_x = x ? c_lo[1] : c_lo[0], c_hi_x = x ? c_hi[1] : c_hi[0];
+          const uint32_t tS = tmem + lane_base + x * kBJ;
+          float m_used = -INFINITY, l_sum = 0.f;
+          bool fast = false;
+          for (int jt = 0; jt < njt && alive; ++jt, ++n) {
             alive = __all_sync(0xffffffffu, mbar_wait(&bars.s_ready[x], n & 1, abort_flag));
             if (!alive) break;
             tc_fence_after();
             if (jt == 0) {
-              // Score bound of this row for the whole k-tile, |A_row| * max_j |K1_j| (log2 units).  Where it is
-              // small for every row of the warp, the bound itself serves as the soft-max reference: P stays
-              // within [2^-2b, 1], representable in the 16-bit type, so the row-maximum pass and every later
-              // rescaling are skipped.  (The two warps that share these rows decide alike: same data, same code.)
               const float bound = sqrtf(norms[(x * 2 + 0) * 128 + row] + norms[(x * 2 + 1) * 128 + row]) * k1_max;
-              fast[x] = __all_sync(0xffffffffu, bound <= p.bound_limit);
-              if (fast[x]) m_used[x] = bound;
+              fast = __all_sync(0xffffffffu, bound <= p.bound_limit);
+              if (fast) m_used = bound;
             }
-            // the last score product of this k-tile has read A_a and A_b
-            if (x == 1 && jt == njt - 1) mbar_arrive(&bars.a_free);
-            const uint32_t tS = tmem + lane_base + x * kBJ + wg * cw;
-            // this row's valid columns among the warpgroup's: [lo, hi]; the warp takes the unmasked code when all its
-            // rows see all of them
-            const int lo = c_lo[x] - j0, hi = c_hi[x] - j0;
-            const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= cw - 1);
-            if (!fast[x]) {
-              // pass 1: row maximum over this warpgroup's columns, then over the slab through the partner warp
-              float mx = nh == 2 ? row_max(std::integral_constant<int, 64>{}, tS, full, lo, hi)
-                                 : row_max(std::integral_constant<int, 32>{}, tS, full, lo, hi);
-              float* slot = xchg + (xphase & 1) * 256;
-              slot[wg * 128 + row] = mx;
-              mbar_arrive(&bars.xchg[wq]);
-              alive = __all_sync(0xffffffffu, mbar_wait(&bars.xchg[wq], xphase & 1, abort_flag));
-              if (!alive) break;
-              mx = fmaxf(mx, slot[(wg ^ 1) * 128 + row]);
-              ++xphase;
+            if (jt == njt - 1) mbar_arrive(&bars.a_free);  // the last score product of this k-tile has read A_x
+            const int hm = halves(ja, jb, (jt0 + jt) * kBJ);
+            const int nh = hm ? 1 : 2, coff = hm == 2 ? 64 : 0;
+            const int j0 = (jt0 + jt) * kBJ + coff;
+            const int lo = c_lo_x - j0, hi = c_hi_x - j0;
+            const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 64 * nh - 1);
+            using N64 = std::integral_constant<int, 64>;
+            if (!fast) {
+              // pass 1: row maximum
+              float mx = row_max(N64{}, tS, full, lo, hi);
+              if (nh == 2) mx = fmaxf(mx, row_max(N64{}, tS + 64, full, lo - 64, hi - 64));
               if (jt == 0) {
-                m_used[x] = mx;  // nothing accumulated yet in this k-tile
+                m_used = mx;  // nothing accumulated yet in this k-tile
               } else {
-                const bool grow = mx > m_used[x] + kRescaleGap;
+                const bool grow = mx > m_used + kRescaleGap;
                 if (__any_sync(0xffffffffu, grow)) {
                   // some row of this warp moved its max up noticeably: rescale accumulator rows (factor 1 for the
-                  // rows that did not move); each warpgroup takes half of the accumulator's columns
-                  const float corr = grow ? exp2f(m_used[x] - mx) : 1.f;
+                  // rows that did not move)
+                  const float corr = grow ? exp2f(m_used - mx) : 1.f;
                   if (grow) {
-                    m_used[x] = mx;
-                    l_sum[x] *= corr;
+                    m_used = mx;
+                    l_sum *= corr;
                   }
                   // (s_ready of this slab was committed after the previous P*V, so that product has landed)
-                  const uint32_t tO = tmem + lane_base + Cfg::kTmemO + x * D + wg * (D / 2);
+                  const uint32_t tO = tmem + lane_base + Cfg::kTmemO + x * D;
 #pragma unroll
-                  for (int ch = 0; ch < D / 64; ++ch) {
+                  for (int ch = 0; ch < D / 32; ++ch) {
                     uint32_t o[32];
                     tmem_ld32(tO + ch * 32, o);
                     tmem_wait_ld();
@@ -543,26 +594,20 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
                 }
               }
             }
-            // pass 2: P = exp2(S - m)
-            l_sum[x] += nh == 2 ? form_p(std::integral_constant<int, 64>{}, tS, full, lo, hi, m_used[x])
-                                : form_p(std::integral_constant<int, 32>{}, tS, full, lo, hi, m_used[x]);
+            // pass 2: P = exp2(S - m), packed to 16 bits over the columns already consumed
+            l_sum += form_p(N64{}, tS, tS, full, lo, hi, m_used);
+            if (nh == 2) l_sum += form_p(N64{}, tS + 64, tS + 32, full, lo - 64, hi - 64, m_used);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars.p_ready[x]);
+            mbar_arrive_n(&bars.p_ready[x], 2);
           }
-        }
-        if (!alive) break;
-        // ---- hand this k-tile's row statistics to the fold warpgroup: (reference, sum of warpgroup 0, of warpgroup 1)
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
+          if (!alive) break;
+          // ---- hand this k-tile's row statistics to the fold warpgroup
           float* srow = stats + (((kt_count & 1) * 2 + x) * 128 + row) * 4;
-          if (wg == 0) {
-            srow[0] = m_used[x];
-            srow[1] = l_sum[x];
-          } else {
-            srow[2] = l_sum[x];
-          }
-          mbar_arrive(&bars.stats_ready[x]);
+          srow[0] = m_used;
+          srow[1] = l_sum;
+          srow[2] = 0.f;
+          mbar_arrive_n(&bars.stats_ready[x], 2);
         }
       }
       if (!alive) break;
@@ -699,26 +744,42 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   if (tid == 0 && bars.abort_flag && p.status) atomicOr(p.status, 2);
 }
 
-// out[bh] = max_j |K1[bh, j, :]|^2 (fp32, compared as integers: non-negative floats order like their bit patterns);
-// a warp per row.  `out` must be zero on entry.
+// Per-head statistics behind the score bounds, a warp per row index r of the three [BN*T, D] tensors:
+//   out[bh] = max_j |K1[bh, j, :]|^2,  out[BN + bh] = max_q |Q[bh, q, :]|^2,  out[2 BN + bh] = max element^2 of K2[bh]
+// (fp32, compared as integers: non-negative floats order like their bit patterns).  `out` must be zero on entry.
 template <typename T16>
-__global__ void k1_norm2_max_kernel(const T16* __restrict__ k1, float* __restrict__ out, size_t rows, int T, int D) {
+__global__ void head_stats_kernel(const T16* __restrict__ k1, const T16* __restrict__ q, const T16* __restrict__ k2,
+                                  float* __restrict__ out, size_t rows, int T, int D, int BN) {
   const size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (r >= rows) return;
-  const uint32_t* src = reinterpret_cast<const uint32_t*>(k1 + r * D);
-  float s = 0.f;
+  const uint32_t* s1 = reinterpret_cast<const uint32_t*>(k1 + r * D);
+  const uint32_t* sq = reinterpret_cast<const uint32_t*>(q + r * D);
+  const uint32_t* s2 = reinterpret_cast<const uint32_t*>(k2 + r * D);
+  float n1 = 0.f, nq = 0.f, e2 = 0.f;
   for (int i = lane; i < D / 2; i += 32) {
-    const float2 f = unpack2<T16>(src[i]);
-    s = fmaf(f.x, f.x, fmaf(f.y, f.y, s));
+    const float2 a = unpack2<T16>(s1[i]), b = unpack2<T16>(sq[i]), c = unpack2<T16>(s2[i]);
+    n1 = fmaf(a.x, a.x, fmaf(a.y, a.y, n1));
+    nq = fmaf(b.x, b.x, fmaf(b.y, b.y, nq));
+    e2 = fmaxf(e2, fmaxf(c.x * c.x, c.y * c.y));
   }
 #pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) atomicMax(reinterpret_cast<int*>(out + r / T), __float_as_int(s));
+  for (int o = 16; o >= 1; o >>= 1) {
+    n1 += __shfl_xor_sync(0xffffffffu, n1, o);
+    nq += __shfl_xor_sync(0xffffffffu, nq, o);
+    e2 = fmaxf(e2, __shfl_xor_sync(0xffffffffu, e2, o));
+  }
+  if (lane == 0) {
+    const size_t bh = r / T;
+    atomicMax(reinterpret_cast<int*>(out + bh), __float_as_int(n1));
+    atomicMax(reinterpret_cast<int*>(out + BN + bh), __float_as_int(nq));
+    atomicMax(reinterpret_cast<int*>(out + 2 * (size_t)BN + bh), __float_as_int(e2));
+  }
 }
 
 // What both forward kernels need before they start: SiLU(V1) in the inputs' type at the head of the workspace and,
-// when the workspace has the optional tail, the per-head largest squared K1 row norm (for the score bound).
+// when the workspace has the optional tail, the per-head statistics of head_stats_kernel (for the score bounds; the
+// returned pointer is to the first of its three arrays of B*N values, the K1 row norms).
 template <typename T16>
 int prepare_fwd(const TdpArgs& a, T16** sv1_out, float** k1n_out) {
   const int BN = a.B * a.N;
@@ -729,11 +790,12 @@ int prepare_fwd(const TdpArgs& a, T16** sv1_out, float** k1n_out) {
   TRITT_CUDA_OK(cudaGetLastError());
   float* k1n = nullptr;
   const size_t tail = align_up(n * 2, 256);
-  if (a.workspace_bytes >= tail + (size_t)BN * sizeof(float)) {
+  if (a.workspace_bytes >= tail + 3 * (size_t)BN * sizeof(float)) {
     k1n = reinterpret_cast<float*>((char*)a.workspace + tail);
-    TRITT_CUDA_OK(cudaMemsetAsync(k1n, 0, (size_t)BN * sizeof(float), a.stream));
+    TRITT_CUDA_OK(cudaMemsetAsync(k1n, 0, 3 * (size_t)BN * sizeof(float), a.stream));
     const size_t rows = (size_t)BN * a.T;
-    k1_norm2_max_kernel<T16><<<(unsigned)((rows + 7) / 8), 256, 0, a.stream>>>((const T16*)a.k1, k1n, rows, a.T, a.D);
+    head_stats_kernel<T16><<<(unsigned)((rows + 7) / 8), 256, 0, a.stream>>>((const T16*)a.k1, (const T16*)a.q,
+                                                                             (const T16*)a.k2, k1n, rows, a.T, a.D, BN);
     count_launch();
     TRITT_CUDA_OK(cudaGetLastError());
   }
@@ -773,6 +835,8 @@ int launch_fwd(const TdpArgs& a) {
   p.kkr = a.mask.kkr;
   p.scale2 = a.alpha * kLog2e;
   p.k1_norm2_max = k1n;
+  p.q_norm2_max = k1n ? k1n + BN : nullptr;
+  p.k2_elem2_max = k1n ? k1n + 2 * BN : nullptr;
   // P = exp2(S - bound) lies in [2^-2 bound, 1]: normal numbers of the 16-bit type (bf16 2^-126, fp16 2^-14)
   p.bound_limit = std::is_same<T16, __nv_bfloat16>::value ? 40.f : 6.f;
   p.status = a.status_word;
@@ -802,7 +866,7 @@ bool sm100_tdp_supported(int op, int T, int D, int dtype, const TdpMask& m) {
 size_t sm100_tdp_fwd_optional_workspace(int B, int N, int T, int D, int dtype) {
   if (dtype != TRITT_BF16 && dtype != TRITT_F16) return 0;
   const size_t n = (size_t)B * N * T * D;
-  return align_up(n * 2, 256) - n * 2 + align_up((size_t)B * N * sizeof(float), 256);
+  return align_up(n * 2, 256) - n * 2 + align_up(3 * (size_t)B * N * sizeof(float), 256);
 }
 
 size_t sm100_tdp_workspace(int op, int B, int N, int T, int D, int dtype) {
