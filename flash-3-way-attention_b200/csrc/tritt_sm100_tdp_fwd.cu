@@ -744,37 +744,55 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   if (tid == 0 && bars.abort_flag && p.status) atomicOr(p.status, 2);
 }
 
-// Per-head statistics behind the score bounds, a warp per row index r of the three [BN*T, D] tensors:
+// Per-head statistics behind the score bounds, over the rows r of the three [BN*T, D] tensors:
 //   out[bh] = max_j |K1[bh, j, :]|^2,  out[BN + bh] = max_q |Q[bh, q, :]|^2,  out[2 BN + bh] = max element^2 of K2[bh]
-// (fp32, compared as integers: non-negative floats order like their bit patterns).  `out` must be zero on entry.
+// (fp32, compared as integers: non-negative floats order like their bit patterns).  A warp takes kStatRows
+// consecutive rows and issues its three atomics once per head it met, not once per row.  `out` must be zero on entry.
+constexpr int kStatRows = 8;
 template <typename T16>
 __global__ void head_stats_kernel(const T16* __restrict__ k1, const T16* __restrict__ q, const T16* __restrict__ k2,
                                   float* __restrict__ out, size_t rows, int T, int D, int BN) {
-  const size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const size_t w = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (r >= rows) return;
-  const uint32_t* s1 = reinterpret_cast<const uint32_t*>(k1 + r * D);
-  const uint32_t* sq = reinterpret_cast<const uint32_t*>(q + r * D);
-  const uint32_t* s2 = reinterpret_cast<const uint32_t*>(k2 + r * D);
-  float n1 = 0.f, nq = 0.f, e2 = 0.f;
-  for (int i = lane; i < D / 2; i += 32) {
-    const float2 a = unpack2<T16>(s1[i]), b = unpack2<T16>(sq[i]), c = unpack2<T16>(s2[i]);
-    n1 = fmaf(a.x, a.x, fmaf(a.y, a.y, n1));
-    nq = fmaf(b.x, b.x, fmaf(b.y, b.y, nq));
-    e2 = fmaxf(e2, fmaxf(c.x * c.x, c.y * c.y));
-  }
+  const size_t r0 = w * kStatRows;
+  if (r0 >= rows) return;
+  const size_t r1 = r0 + kStatRows < rows ? r0 + kStatRows : rows;
+  float m1 = 0.f, mq = 0.f, m2 = 0.f;   // maxima over the rows of the current head
+  size_t bh = r0 / T;
+  auto flush = [&]() {
+    if (lane == 0) {
+      atomicMax(reinterpret_cast<int*>(out + bh), __float_as_int(m1));
+      atomicMax(reinterpret_cast<int*>(out + BN + bh), __float_as_int(mq));
+      atomicMax(reinterpret_cast<int*>(out + 2 * (size_t)BN + bh), __float_as_int(m2));
+    }
+  };
+  for (size_t r = r0; r < r1; ++r) {
+    if (r / T != bh) {
+      flush();
+      bh = r / T;
+      m1 = mq = m2 = 0.f;
+    }
+    const uint32_t* s1 = reinterpret_cast<const uint32_t*>(k1 + r * D);
+    const uint32_t* sq = reinterpret_cast<const uint32_t*>(q + r * D);
+    const uint32_t* s2 = reinterpret_cast<const uint32_t*>(k2 + r * D);
+    float n1 = 0.f, nq = 0.f, e2 = 0.f;
+    for (int i = lane; i < D / 2; i += 32) {
+      const float2 a = unpack2<T16>(s1[i]), b = unpack2<T16>(sq[i]), c = unpack2<T16>(s2[i]);
+      n1 = fmaf(a.x, a.x, fmaf(a.y, a.y, n1));
+      nq = fmaf(b.x, b.x, fmaf(b.y, b.y, nq));
+      e2 = fmaxf(e2, fmaxf(c.x * c.x, c.y * c.y));
+    }
 #pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) {
-    n1 += __shfl_xor_sync(0xffffffffu, n1, o);
-    nq += __shfl_xor_sync(0xffffffffu, nq, o);
-    e2 = fmaxf(e2, __shfl_xor_sync(0xffffffffu, e2, o));
+    for (int o = 16; o >= 1; o >>= 1) {
+      n1 += __shfl_xor_sync(0xffffffffu, n1, o);
+      nq += __shfl_xor_sync(0xffffffffu, nq, o);
+      e2 = fmaxf(e2, __shfl_xor_sync(0xffffffffu, e2, o));
+    }
+    m1 = fmaxf(m1, n1);
+    mq = fmaxf(mq, nq);
+    m2 = fmaxf(m2, e2);
   }
-  if (lane == 0) {
-    const size_t bh = r / T;
-    atomicMax(reinterpret_cast<int*>(out + bh), __float_as_int(n1));
-    atomicMax(reinterpret_cast<int*>(out + BN + bh), __float_as_int(nq));
-    atomicMax(reinterpret_cast<int*>(out + 2 * (size_t)BN + bh), __float_as_int(e2));
-  }
+  flush();
 }
 
 // What both forward kernels need before they start: SiLU(V1) in the inputs' type at the head of the workspace and,
@@ -794,7 +812,8 @@ int prepare_fwd(const TdpArgs& a, T16** sv1_out, float** k1n_out) {
     k1n = reinterpret_cast<float*>((char*)a.workspace + tail);
     TRITT_CUDA_OK(cudaMemsetAsync(k1n, 0, 3 * (size_t)BN * sizeof(float), a.stream));
     const size_t rows = (size_t)BN * a.T;
-    head_stats_kernel<T16><<<(unsigned)((rows + 7) / 8), 256, 0, a.stream>>>((const T16*)a.k1, (const T16*)a.q,
+    const size_t warps = (rows + kStatRows - 1) / kStatRows;
+    head_stats_kernel<T16><<<(unsigned)((warps + 7) / 8), 256, 0, a.stream>>>((const T16*)a.k1, (const T16*)a.q,
                                                                              (const T16*)a.k2, k1n, rows, a.T, a.D, BN);
     count_launch();
     TRITT_CUDA_OK(cudaGetLastError());

@@ -72,7 +72,7 @@ unsigned long long tritt_kernel_launches(void);
 const char* tritt_last_error(void);
 
 /* Bytes of caller-provided scratch to pass to the given operation (0 if none).  For TRITT_OP_TDP_FWD on 16-bit inputs
-   the figure includes a small tail (one float per (batch, head), behind the SiLU(V1) copy of B*N*T*D elements) that
+   the figure includes a small tail (three floats per (batch, head), behind the SiLU(V1) copy of B*N*T*D elements) that
    lets the forward bound its scores and skip the row-maximum pass; a workspace without the tail is accepted and runs
    the two-pass soft-max. */
 size_t tritt_workspace_bytes(int op, int B, int N, int T, int D, int dtype);
