@@ -48,10 +48,7 @@ constexpr int kBC = 128;  // key columns per slab
 
 template <int D> struct BwdCfg {
   static constexpr int kTileA = 128 * D * 2;   // one 128-row operand / key / value tile
-  // At head dimension 64 the accumulators leave room for a second score buffer in tensor memory: S(c+2) is issued
-  // while the soft-max warps still work on slab c, and the ring of column tiles is twice as deep to feed it.
-  static constexpr int kSBuf = D == 64 ? 2 : 1;
-  static constexpr int kStages = 4 * kSBuf;    // ring of column tiles: Kc(c), Vc(c), Kc(c+1), Vc(c+1), ...
+  static constexpr int kStages = 4;            // ring of column tiles: Kc(c), Vc(c), Kc(c+1), Vc(c+1)
   static constexpr int kOffA = 0;              // A  (row-key pre-product)
   static constexpr int kOffA2 = kTileA;        // A' (row-value pre-product)
   static constexpr int kOffRing = 2 * kTileA;
@@ -61,8 +58,8 @@ template <int D> struct BwdCfg {
   static constexpr int kOffVec = kOffDq + D * 4;                 // [2 parities][2][D] fp32: Q[q], dO[q]
   static constexpr int kOffMisc = kOffVec + 4 * D * 4;           // [4] fp32: Dq partials
   static constexpr int kOffBars = kOffMisc + 16;                 // barriers (no static shared memory is used, so
-  static constexpr int kSmem = kOffBars + 288;                   //  the dynamic region starts 1024-byte aligned)
-  static constexpr int kTmemS = 0, kTmemDP = 128 * kSBuf, kTmemG = kTmemDP + 128, kTmemU = kTmemG + D;
+  static constexpr int kSmem = kOffBars + 208;                   //  the dynamic region starts 1024-byte aligned)
+  static constexpr int kTmemS = 0, kTmemDP = 128, kTmemG = 256, kTmemU = 256 + D;
 };
 
 // NSW soft-max warpgroups (2 or 4) + 4 service warps (TMA, MMA, 2 idle) + the fold warpgroup
@@ -84,9 +81,9 @@ struct BwdParams {
 };
 
 struct BwdBarriers {
-  uint64_t ring_full[8], ring_empty[8];
+  uint64_t ring_full[4], ring_empty[4];
   uint64_t xy_full, ax_ready, ay_ready, a_free;  // A (score operand) and A' (dP operand) become ready separately
-  uint64_t s_ready[2], dp_ready, p_ready[2], ds_ready;  // slab hand-offs (per score buffer; P in two column halves)
+  uint64_t s_ready, dp_ready, p_ready[2], ds_ready;  // slab hand-offs (P in two column halves)
   uint64_t gu_done, u_free, g_free;               // tile hand-offs with the fold warpgroup (U is drained first)
   uint64_t sm_sync, fold_sync;
   uint64_t vec_free[2];                           // fold warpgroup -> soft-max: a copy of Q[q] / dO[q] is no longer read
@@ -134,8 +131,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   constexpr int kFoldWarp0 = BwdThreads<NSW>::kFoldWarp0;
   constexpr int CW = kBC / NSW;  // slab columns owned by one soft-max warpgroup
   extern __shared__ __align__(1024) uint8_t smem[];
-  static_assert(sizeof(BwdBarriers) <= 288, "barrier block too large");
-  constexpr int kSBuf = Cfg::kSBuf;
+  static_assert(sizeof(BwdBarriers) <= 208, "barrier block too large");
   BwdBarriers& bars = *reinterpret_cast<BwdBarriers*>(smem + Cfg::kOffBars);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (smem_u32(smem) & 1023u) {
@@ -157,8 +153,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     mbar_init(&bars.ax_ready, kToMmaSm);
     mbar_init(&bars.ay_ready, kToMmaSm);
     mbar_init(&bars.a_free, kNumSoftmax);
-    mbar_init(&bars.s_ready[0], 1);
-    mbar_init(&bars.s_ready[1], 1);
+    mbar_init(&bars.s_ready, 1);
     mbar_init(&bars.dp_ready, 1);
     mbar_init(&bars.p_ready[0], kToMmaSm);
     mbar_init(&bars.p_ready[1], kToMmaSm);
@@ -354,15 +349,15 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       };
       // One 8-instruction accumulation chain each (D = 128): S = A Kc^T, dP = A' Vc^T (operands in shared
       // memory, key/value tile K-major), U (+)= P Vc, G (+)= dS Kc (P / dS from tensor memory, the tile row-major).
-      auto issue_s = [&](uint32_t pos, int buf) -> bool {
+      auto issue_s = [&](uint32_t pos) -> bool {
         if (!wait_full(pos)) return false;
         const uint32_t bLo = ringK + (pos % NS) * kTile16;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2, kb = (k >> 2) * kBlkK + (k & 3) * 2;
-          mma_ss_any(tmem + Cfg::kTmemS + buf * 128, aLo + kk, bLo + kb, idesc_s, k > 0);
+          mma_ss_any(tmem + Cfg::kTmemS, aLo + kk, bLo + kb, idesc_s, k > 0);
         }
-        commit(&bars.s_ready[buf]);
+        commit(&bars.s_ready);
         return true;
       };
       auto issue_dp = [&](uint32_t pos) -> bool {
@@ -380,13 +375,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       constexpr int KPW = CW / 16;  // 16-deep MMA steps per warpgroup
       // U is issued in two halves: the k-steps fed by the first half of every warpgroup's columns as soon as
       // that half of P is there, the rest when the second half arrives (same accumulation chain).
-      auto issue_u_half = [&](uint32_t pos, uint32_t acc, int half, int buf) {
+      auto issue_u_half = [&](uint32_t pos, uint32_t acc, int half) {
         const uint32_t st = pos % NS;
         bool first = half == 0;
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
           if (((k % KPW) >= KPW / 2) != (half == 1)) continue;
-          const uint32_t a = tmem + Cfg::kTmemS + buf * 128 + (k / KPW) * CW + (k % KPW) * 8;
+          const uint32_t a = tmem + Cfg::kTmemS + (k / KPW) * CW + (k % KPW) * 8;
           mma_ts_any(tmem + Cfg::kTmemU, a, ringMN + st * kTile16 + k * (2048 >> 4), idesc_g, first ? acc : 1u);
           first = false;
         }
@@ -413,27 +408,23 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           // the first score product starts while the soft-max warps still form the dP operand
           if (!mbar_wait_x<PAIR>(&bars.ax_ready, xt_count & 1, abort_flag)) { alive = false; break; }
           tc_fence_after();
-          if (!issue_s(base, 0)) { alive = false; break; }
+          if (!issue_s(base)) { alive = false; break; }
           if (!mbar_wait_x<PAIR>(&bars.ay_ready, xt_count & 1, abort_flag)) { alive = false; break; }
           tc_fence_after();
           if (!issue_dp(base + 1)) { alive = false; break; }
-          // (with two score buffers the second slab's scores follow at once)
-          if (kSBuf == 2 && ncs > 1 && !issue_s(base + 2, 1)) { alive = false; break; }
           for (int c = 0; c < ncs && alive; ++c, ++n) {
             const bool more = c + 1 < ncs;
-            const int buf = c % kSBuf;
             if (!mbar_wait_x<PAIR>(&bars.p_ready[0], n & 1, abort_flag)) { alive = false; break; }
             if (c == 0) {
               // the fold warpgroup must have drained the previous tile's U
               if (!mbar_wait_x<PAIR>(&bars.u_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
             }
             tc_fence_after();
-            issue_u_half(base + 2 * c + 1, c > 0, 0, buf);
+            issue_u_half(base + 2 * c + 1, c > 0, 0);
             if (!mbar_wait_x<PAIR>(&bars.p_ready[1], n & 1, abort_flag)) { alive = false; break; }
             tc_fence_after();
-            issue_u_half(base + 2 * c + 1, c > 0, 1, buf);
-            // the buffer P(c) sits in is free again once U(c) has run: the scores of slab c + kSBuf go there
-            if (c + kSBuf < ncs && !issue_s(base + 2 * (c + kSBuf), buf)) { alive = false; break; }
+            issue_u_half(base + 2 * c + 1, c > 0, 1);
+            if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
             if (!mbar_wait_x<PAIR>(&bars.ds_ready, n & 1, abort_flag)) { alive = false; break; }
             if (c == 0) {
               // ... and the previous tile's G
@@ -457,7 +448,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     float* vec = (float*)(smem + Cfg::kOffVec);
     float* misc = (float*)(smem + Cfg::kOffMisc);
     uint32_t xt_count = 0, n = 0, sync_phase = 0, item_count = 0;
-    uint32_t s_use0 = 0, s_use1 = 0;   // score products consumed so far, per score buffer
     bool alive = true;
     auto sm_sync = [&]() -> bool {
       mbar_arrive(&bars.sm_sync);
@@ -551,19 +541,15 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           c_lo = max(q - win.cw, x_r - win.below);
           c_hi = row_valid ? min(q, x_r + win.above) : c_lo - 1;
         }
-        const uint32_t tS0 = tmem + lane_base + Cfg::kTmemS + wg * CW;
+        const uint32_t tS = tmem + lane_base + Cfg::kTmemS + wg * CW;
         const uint32_t tDP = tmem + lane_base + Cfg::kTmemDP + wg * CW;
 
         for (int c = 0; c < ncs; ++c, ++n) {
           const int lo = c_lo - (c0 + c) * kBC - wg * CW, hi = c_hi - (c0 + c) * kBC - wg * CW;
           uint32_t pk[CW / 2];
           // ---- S -> P
-          const int buf = c % kSBuf;
-          const uint32_t tS = tS0 + buf * 128;
-          const uint32_t s_use = buf ? s_use1 : s_use0;
-          alive = __all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.s_ready[buf], s_use & 1, abort_flag));
+          alive = __all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.s_ready, n & 1, abort_flag));
           if (!alive) break;
-          if (buf) ++s_use1; else ++s_use0;
           tc_fence_after();
           static_assert(CW == 64, "the two-half hand-off of P is written for two soft-max warpgroups");
           // (the read of the second half is in flight while the first half is worked on)
