@@ -34,6 +34,35 @@ def _fwd_case(B, N, T, D, dtype, causal, scale_in, alpha, seed, o_scale=1.0):
 
 
 @pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("windows", [(None, None, None, None), (100, 70, 40, 30)])
+def test_forward_heads_with_small_and_large_logits_in_one_launch(D, dtype, windows):
+    """The forward picks the soft-max warps' organisation per head from a head-wide score bound (column split with
+    the row's bound as reference / one warpgroup per tile with row maxima).  Heads of both kinds alternate here, so
+    every CTA changes organisation between consecutive work items and the same barriers serve both."""
+    B, N, T, alpha = 1, 6, 300, 1 / 8
+    q, k1, k2, v1, v2, _ = orc.make_inputs(B, N, T, D, scale=1.0, seed=41 + D, dtype=torch.float32)
+    head_scale = torch.tensor([0.25, 1.5, 0.25, 1.5, 1.5, 0.25]).view(1, N, 1, 1)
+    q, k1, k2 = ((t * head_scale).to(dtype) for t in (q, k1, k2))
+    v1, v2 = v1.to(dtype), v2.to(dtype)
+    dev = [t.to(DEV) for t in (q, k1, k2, v1, v2)]
+    o = torch.empty_like(dev[0])
+    lse = torch.empty(B, N, T, device=DEV)
+    _native.tdp_fwd(*dev, o, lse, alpha, True, *windows)
+    torch.cuda.synchronize()
+    assert _native.read_status(torch.device(DEV)) == 0, "a bounded barrier wait ran out"
+    z_ref, lse_ref = orc.tdp_forward(*(t.float() for t in (q, k1, k2, v1, v2)), alpha, True, *windows)
+    for h in range(N):   # per head: the large-logit heads would otherwise hide the small ones
+        assert_close(f"o[head {h}]", o[:, h].cpu(), z_ref[:, h], dtype)
+    # The log-sum-exp carries the absolute rounding error of the row's largest logit (one 16-bit rounding of the
+    # operand A: 2^-9 relative for bf16); the large-logit heads reach |logit| ~ 25, hence five times the usual bound.
+    tol = 2e-2 if dtype == torch.bfloat16 else 5e-3
+    lerr = (lse.cpu() - lse_ref).abs().amax(dim=(0, 2))
+    for h in range(N):
+        assert float(lerr[h]) <= tol * (5.0 if float(head_scale[0, h, 0, 0]) > 1 else 1.0), (h, float(lerr[h]))
+
+
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("T", [40, 64, 100, 129, 256, 333])
 @pytest.mark.parametrize("causal", [True, False])
 def test_forward_bf16_matches_oracle(T, D, causal):
