@@ -83,6 +83,13 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def wait_first(self, timeout: float = 8.0):
+        """Returns once the sampler has printed its first line (its start-up enumerates every GPU of the machine and
+        can hold up kernel launches for hundreds of milliseconds, which must not fall into a timed region)."""
+        t0 = time.time()
+        while self.proc is not None and not self.lines and time.time() - t0 < timeout and self.proc.poll() is None:
+            time.sleep(0.02)
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -434,6 +441,9 @@ def run_ours(args):
             ms = float(t.item())
         return ms / steps
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     warmup = max(args.warmup, 1)
     for _ in range(warmup):
         step_resident()
@@ -454,9 +464,9 @@ def run_ours(args):
         fwd_ms.append(ev[0].elapsed_time(ev[1]))
         bwd_ms.append(ev[1].elapsed_time(ev[2]))
 
-    sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
+        sampler.wait_first()
+        sampler.lines.clear()   # keep the samples of the timed regions only
     l0 = _native.lib().tritt_kernel_launches()
     ms_res = timed(step_resident, args.steps)
     launches = _native.lib().tritt_kernel_launches() - l0
