@@ -319,7 +319,12 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && rank == 0) {
+    // The whole warp walks the schedule in step and one elected lane issues: with converged control flow the
+    // descriptor arithmetic stays on the uniform datapath, where a lone thread needs a register-to-uniform move
+    // per operand and loses its issue slots to the busy warps of its scheduler (a stand-alone loop of these chains
+    // under issue pressure: 15.3 k cycles per 32 instructions from one thread, 3.9 k from a converged warp).
+    if (rank == 0) {
+      const bool leader = elect_one();
       constexpr int kFmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
       constexpr int kM = PAIR ? 256 : 128;   // rows of one instruction (both CTAs of a pair)
       constexpr uint32_t idesc_s = make_idesc_f16(kM, kBC, kFmt, false, false);
@@ -334,18 +339,25 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       // K-major view: 64-column blocks of a tile are 16 KB apart, of a pair's 64-row half 8 KB
       constexpr uint32_t kBlkK = (PAIR ? 8192 : 16384) >> 4;
       auto commit = [&](uint64_t* bar) {
+        if (!leader) return;
         if constexpr (PAIR) mma_commit_pair(bar); else mma_commit(bar);
       };
       auto mma_ss_any = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+        if (!leader) return;
         if constexpr (PAIR) mma_ss_lo_pair(d, a_lo, b_lo, kHi, idesc, acc); else mma_ss_lo(d, a_lo, b_lo, kHi, idesc, acc);
       };
       auto mma_ts_any = [&](uint32_t d, uint32_t a_t, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+        if (!leader) return;
         if constexpr (PAIR) mma_ts_lo_pair(d, a_t, b_lo, kHi, idesc, acc); else mma_ts_lo(d, a_t, b_lo, kHi, idesc, acc);
+      };
+      // (every lane waits; the vote keeps the warp converged whatever a lane's wait returned)
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, mbar_wait_x<PAIR>(bar, parity, abort_flag));
       };
       uint32_t xt_count = 0, base = 0, n = 0;
       bool alive = true;
       auto wait_full = [&](uint32_t pos) {
-        return mbar_wait_x<PAIR>(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
+        return wait_all(&bars.ring_full[pos % NS], (pos / NS) & 1);
       };
       // One 8-instruction accumulation chain each (D = 128): S = A Kc^T, dP = A' Vc^T (operands in shared
       // memory, key/value tile K-major), U (+)= P Vc, G (+)= dS Kc (P / dS from tensor memory, the tile row-major).
@@ -406,29 +418,29 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           int c0, ncs;
           c_range(qr, win, xt, c0, ncs);
           // the first score product starts while the soft-max warps still form the dP operand
-          if (!mbar_wait_x<PAIR>(&bars.ax_ready, xt_count & 1, abort_flag)) { alive = false; break; }
+          if (!wait_all(&bars.ax_ready, xt_count & 1)) { alive = false; break; }
           tc_fence_after();
           if (!issue_s(base)) { alive = false; break; }
-          if (!mbar_wait_x<PAIR>(&bars.ay_ready, xt_count & 1, abort_flag)) { alive = false; break; }
+          if (!wait_all(&bars.ay_ready, xt_count & 1)) { alive = false; break; }
           tc_fence_after();
           if (!issue_dp(base + 1)) { alive = false; break; }
           for (int c = 0; c < ncs && alive; ++c, ++n) {
             const bool more = c + 1 < ncs;
-            if (!mbar_wait_x<PAIR>(&bars.p_ready[0], n & 1, abort_flag)) { alive = false; break; }
+            if (!wait_all(&bars.p_ready[0], n & 1)) { alive = false; break; }
             if (c == 0) {
               // the fold warpgroup must have drained the previous tile's U
-              if (!mbar_wait_x<PAIR>(&bars.u_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+              if (!wait_all(&bars.u_free, (xt_count & 1) ^ 1)) { alive = false; break; }
             }
             tc_fence_after();
             issue_u_half(base + 2 * c + 1, c > 0, 0);
-            if (!mbar_wait_x<PAIR>(&bars.p_ready[1], n & 1, abort_flag)) { alive = false; break; }
+            if (!wait_all(&bars.p_ready[1], n & 1)) { alive = false; break; }
             tc_fence_after();
             issue_u_half(base + 2 * c + 1, c > 0, 1);
             if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
-            if (!mbar_wait_x<PAIR>(&bars.ds_ready, n & 1, abort_flag)) { alive = false; break; }
+            if (!wait_all(&bars.ds_ready, n & 1)) { alive = false; break; }
             if (c == 0) {
               // ... and the previous tile's G
-              if (!mbar_wait_x<PAIR>(&bars.g_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+              if (!wait_all(&bars.g_free, (xt_count & 1) ^ 1)) { alive = false; break; }
             }
             tc_fence_after();
             issue_g(base + 2 * c, c > 0);

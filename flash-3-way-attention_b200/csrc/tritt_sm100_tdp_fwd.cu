@@ -239,7 +239,18 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the schedule in step and one elected lane issues: with converged control flow the
+    // descriptor arithmetic stays on the uniform datapath, where a lone thread needs a register-to-uniform move per
+    // operand and loses its issue slots to the busy warps of its scheduler.
+    {
+      const bool leader = elect_one();
+      // (every lane waits; the vote keeps the warp converged whatever a lane's wait returned)
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (leader) mma_commit(bar);
+      };
       constexpr int kFmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = make_idesc_f16(128, kBJ, kFmt, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, D, kFmt, false, true);
@@ -252,9 +263,9 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       uint32_t kt_count = 0, base = 0, n = 0;  // n: slabs finished so far (same for both tiles)
       bool alive = true;
       auto wait_full = [&](uint32_t pos) {
-        return mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag);
+        return wait_all(&bars.ring_full[pos % NS], (pos / NS) & 1);
       };
-      auto release = [&](uint32_t pos) { mma_commit(&bars.ring_empty[pos % NS]); };
+      auto release = [&](uint32_t pos) { commit(&bars.ring_empty[pos % NS]); };
       // S_x = A_x * K1tile^T  (one chain of D/16 instructions); hm != 0: only 64 rows of the key tile (the lower
       // or the upper ones), scores in the first 64 columns of S_x
       constexpr uint32_t idesc_s64 = make_idesc_f16(128, 64, kFmt, false, false);
@@ -264,17 +275,17 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-            mma_ss_lo(tmem + x * kBJ, aLo[x] + kk, bLo + kk, kHi, idesc_s, k > 0);
+            if (leader) mma_ss_lo(tmem + x * kBJ, aLo[x] + kk, bLo + kk, kHi, idesc_s, k > 0);
           }
         } else {
           const uint32_t bRow = bLo + (hm == 2 ? (64 * 128) >> 4 : 0);   // rows 64.. of a 128-byte-pitch block
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-            mma_ss_lo(tmem + x * kBJ, aLo[x] + kk, bRow + kk, kHi, idesc_s64, k > 0);
+            if (leader) mma_ss_lo(tmem + x * kBJ, aLo[x] + kk, bRow + kk, kHi, idesc_s64, k > 0);
           }
         }
-        mma_commit(&bars.s_ready[x]);
+        commit(&bars.s_ready[x]);
       };
       // acc_x (+)= P_x * SiLU(V1)tile  (one chain of 8 instructions; P_x overlays the first 64 columns of S_x);
       // hm != 0: P_x has 64 columns (4 instructions) and meets the lower or upper 64 rows of the value tile
@@ -284,13 +295,15 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         if (hm == 0) {
 #pragma unroll
           for (int k = 0; k < kBJ / 16; ++k)
-            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (split ? (k >> 2) * 64 + (k & 3) * 8 : k * 8),
+            if (leader)
+              mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (split ? (k >> 2) * 64 + (k & 3) * 8 : k * 8),
                       bLo + k * (2048 >> 4), kHi, idesc_pv, k > 0 ? 1u : acc);
         } else {
           const uint32_t bRow = bLo + (hm == 2 ? (4 * 2048) >> 4 : 0);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (split ? (k >> 1) * 32 + (k & 1) * 8 : k * 8),
+            if (leader)
+              mma_ts_lo(tmem + Cfg::kTmemO + x * D, tmem + x * kBJ + (split ? (k >> 1) * 32 + (k & 1) * 8 : k * 8),
                       bRow + k * (2048 >> 4), kHi, idesc_pv, k > 0 ? 1u : acc);
         }
       };
@@ -303,7 +316,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
         for (int kt = kt0; kt < kt0 + nkt && alive; ++kt, ++kt_count) {
           int jt0, njt;
           j_range(qa, qb, kt, jt0, njt);
-          if (!mbar_wait(&bars.a_ready, kt_count & 1, abort_flag)) { alive = false; break; }
+          if (!wait_all(&bars.a_ready, kt_count & 1)) { alive = false; break; }
           tc_fence_after();
           if (!wait_full(base)) { alive = false; break; }
           int ja, jb;
@@ -317,10 +330,10 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             const bool more = jt + 1 < njt;
             const int hm_next = more ? halves(ja, jb, (jt0 + jt + 1) * kBJ) : 0;
             for (int x = 0; x < 2 && alive; ++x) {
-              if (!mbar_wait(&bars.p_ready[x], n & 1, abort_flag)) { alive = false; break; }
+              if (!wait_all(&bars.p_ready[x], n & 1)) { alive = false; break; }
               if (jt == 0) {
                 // the fold warpgroup must have drained the previous k-tile's accumulator of this tile
-                if (!mbar_wait(&bars.o_free[x], (kt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
+                if (!wait_all(&bars.o_free[x], (kt_count & 1) ^ 1)) { alive = false; break; }
               }
               tc_fence_after();
               if (x == 0 && !wait_full(pv)) { alive = false; break; }
@@ -334,7 +347,7 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             }
             hm = hm_next;
           }
-          if (alive) mma_commit(&bars.o_done);
+          if (alive) commit(&bars.o_done);
           base += 2 * njt;
         }
       }
