@@ -208,7 +208,16 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (the whole warp walks the schedule converged and one elected lane issues: the descriptor arithmetic stays on
+    //  the uniform datapath)
+    {
+      const bool leader = elect_one();
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (leader) mma_commit(bar);
+      };
       constexpr int kFmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = make_idesc_f16(128, 128, kFmt, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, D, kFmt, false, true);
@@ -223,35 +232,35 @@ tdp_fwd_band_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_const
       auto issue_pv = [&](uint32_t tt) -> bool {
         const int x = tt & 1;
         const uint32_t u = tt >> 1, pos = 2 * tt + 1;
-        if (!mbar_wait(&bars.p_ready[x], u & 1, abort_flag)) return false;
+        if (!wait_all(&bars.p_ready[x], u & 1)) return false;
         // the fold warpgroup must have drained this slot's accumulator of two tiles ago
-        if (!mbar_wait(&bars.o_free[x], (u & 1) ^ 1, abort_flag)) return false;
-        if (!mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag)) return false;
+        if (!wait_all(&bars.o_free[x], (u & 1) ^ 1)) return false;
+        if (!wait_all(&bars.ring_full[pos % NS], (pos / NS) & 1)) return false;
         tc_fence_after();
         const uint32_t bLo = ringMN + (pos % NS) * kTile16;
         // (always the full chain of 8: columns of P beyond the attended range are zero, and a loop with a run-time
         //  bound costs the issuing thread more than the skipped instructions save)
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          mma_ts_lo(tmem + Cfg::kTmemAcc + x * D, tmem + x * 128 + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv, k > 0);
-        mma_commit(&bars.o_done[x]);
-        mma_commit(&bars.ring_empty[pos % NS]);
+          if (leader) mma_ts_lo(tmem + Cfg::kTmemAcc + x * D, tmem + x * 128 + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv, k > 0);
+        commit(&bars.o_done[x]);
+        commit(&bars.ring_empty[pos % NS]);
         return true;
       };
       for_each_tile([&](const BandTile& t, uint32_t ti) {
         const int x = ti & 1;
         const uint32_t u = ti >> 1, pos = 2 * ti;
-        if (!mbar_wait(&bars.a_ready[x], u & 1, abort_flag)) return alive = false;
-        if (!mbar_wait(&bars.ring_full[pos % NS], (pos / NS) & 1, abort_flag)) return alive = false;
+        if (!wait_all(&bars.a_ready[x], u & 1)) return alive = false;
+        if (!wait_all(&bars.ring_full[pos % NS], (pos / NS) & 1)) return alive = false;
         tc_fence_after();
         const uint32_t bLo = ringK + (pos % NS) * kTile16;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-          mma_ss_lo(tmem + x * 128, aLo[x] + kk, bLo + kk, kHi, idesc_s, k > 0);
+          if (leader) mma_ss_lo(tmem + x * 128, aLo[x] + kk, bLo + kk, kHi, idesc_s, k > 0);
         }
-        mma_commit(&bars.s_ready[x]);
-        mma_commit(&bars.ring_empty[pos % NS]);
+        commit(&bars.s_ready[x]);
+        commit(&bars.ring_empty[pos % NS]);
         if (ti > 0 && !issue_pv(ti - 1)) return alive = false;
         n_tiles = ti + 1;
         return true;
