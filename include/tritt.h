@@ -59,8 +59,8 @@ enum {
   TRITT_FLAG_BWD_CTA_PAIRS = 8  /* tritt_tdp_bwd, 16-bit inputs, head dimension 128, no windows, an even number of
                                  queries: run the backward kernel as clusters of two CTAs that share every key / value
                                  tile (tcgen05 cta_group::2, 256-row products).  Same results up to the order of the
-                                 fp32 reduce-adds; measured 0.4 % slower per step than one CTA per item on a B200, so
-                                 it is not the default.  Ignored where it does not apply. */
+                                 fp32 reduce-adds; measured 2 % slower than one CTA per item on a B200, so it is not
+                                 the default.  Ignored where it does not apply. */
 };
 
 /* kernel families, as reported by tritt_tdp_path() */
