@@ -20,7 +20,7 @@
 //
 // Tensor-core usage follows what the hardware rewards: 128-column slabs, so that every
 // accumulation chain is 8 instructions of 128x128x16 (an instruction below N = 128 costs the same
-// ~48-64 cycles, and every change of accumulator costs the pipe ~120 cycles), TMEM fully used
+// ~48-64 cycles), TMEM fully used
 // as S | dP | G | U (4 x 128 columns at D = 128).  P and dS are written back as 16-bit into the
 // first half of the S and dP column ranges and feed the G / U products from tensor memory.
 //
