@@ -152,7 +152,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     constexpr uint32_t kToMmaSm = PAIR ? 2 * kNumSoftmax / 32 : kNumSoftmax, kToMmaFold = PAIR ? 2 * 4 : 128;
     mbar_init(&bars.ax_ready, kToMmaSm);
     mbar_init(&bars.ay_ready, kToMmaSm);
-    mbar_init(&bars.a_free, kNumSoftmax);
+    mbar_init(&bars.a_free, 1);   // a commit behind the tile's last score / dP products
     mbar_init(&bars.s_ready, 1);
     mbar_init(&bars.dp_ready, 1);
     mbar_init(&bars.p_ready[0], kToMmaSm);
@@ -424,6 +424,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           if (!wait_all(&bars.ay_ready, xt_count & 1)) { alive = false; break; }
           tc_fence_after();
           if (!issue_dp(base + 1)) { alive = false; break; }
+          // Once the tile's last S and dP products have run, its operand tiles may be reloaded: the commit lets the
+          // producer fetch the next tile's rows a slab before the soft-max warps are done with this one.
+          if (ncs == 1) commit(&bars.a_free);
           for (int c = 0; c < ncs && alive; ++c, ++n) {
             const bool more = c + 1 < ncs;
             if (!wait_all(&bars.p_ready[0], n & 1)) { alive = false; break; }
@@ -445,6 +448,7 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
             tc_fence_after();
             issue_g(base + 2 * c, c > 0);
             if (more && !issue_dp(base + 2 * (c + 1) + 1)) { alive = false; break; }
+            if (c + 2 == ncs) commit(&bars.a_free);   // that was the tile's last dP (its last S went before it)
           }
           if (alive) commit(&bars.gu_done);
           base += 2 * ncs;
@@ -599,10 +603,6 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           alive = __all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.dp_ready, n & 1, abort_flag));
           if (!alive) break;
           tc_fence_after();
-          if (c == ncs - 1) {
-            // every S / dP product of this tile has completed: the operand tiles may be reloaded
-            mbar_arrive(&bars.a_free);
-          }
           uint32_t dk[CW / 2];
           {
             uint32_t dp[CW];
