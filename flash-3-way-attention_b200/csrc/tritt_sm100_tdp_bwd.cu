@@ -252,9 +252,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      const CUtensorMap* maps[8] = {&tmK1, &tmK2, &tmSV1, &tmV2, &tmDK1, &tmDK2, &tmDSV1, &tmDV2};
-      for (int i = 0; i < 8; ++i) tma_prefetch_desc(maps[i]);
+    // (like the MMA warp: the whole warp walks the schedule converged, one elected lane issues the copies)
+    {
+      const bool leader = elect_one();
+      if (leader) {
+        const CUtensorMap* maps[8] = {&tmK1, &tmK2, &tmSV1, &tmV2, &tmDK1, &tmDK2, &tmDSV1, &tmDV2};
+        for (int i = 0; i < 8; ++i) tma_prefetch_desc(maps[i]);
+      }
       uint32_t xt_count = 0, pos = 0;
       bool alive = true;
       // One column tile (128 rows of Kc or Vc) into the next ring stage.  In a pair each CTA fetches what its half
@@ -263,17 +267,20 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       // bytes of both CTAs are counted on the even CTA's barrier, where the issuing thread waits.
       auto load_stage = [&](const CUtensorMap* tm, const CUtensorMap* tm_half, int row0, int bh) -> bool {
         const int st = pos % NS;
-        if (!mbar_wait_x<PAIR>(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag)) return false;
+        if (!__all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag)))
+          return false;
         uint8_t* dst = smem + Cfg::kOffRing + st * Cfg::kTileA;
-        if constexpr (PAIR) {
-          if (rank == 0) mbar_arrive_expect_tx(&bars.ring_full[st], 2 * Cfg::kTileA);
-          const uint32_t full0 = mbar_in_cta(&bars.ring_full[st], 0);
-          tma_load_3d_pair(dst, tm_half, full0, 0, row0 + 64 * (int)rank, bh);
-          tma_load_3d_pair(dst + 8192, tm_half, full0, 64, row0 + 64 * (int)rank, bh);
-          tma_load_3d_pair(dst + 16384, tm, full0, 64 * (int)rank, row0, bh);
-        } else {
-          mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kTileA);
-          for (int hh = 0; hh < KH; ++hh) tma_load_3d(dst + hh * 16384, tm, &bars.ring_full[st], hh * 64, row0, bh);
+        if (leader) {
+          if constexpr (PAIR) {
+            if (rank == 0) mbar_arrive_expect_tx(&bars.ring_full[st], 2 * Cfg::kTileA);
+            const uint32_t full0 = mbar_in_cta(&bars.ring_full[st], 0);
+            tma_load_3d_pair(dst, tm_half, full0, 0, row0 + 64 * (int)rank, bh);
+            tma_load_3d_pair(dst + 8192, tm_half, full0, 64, row0 + 64 * (int)rank, bh);
+            tma_load_3d_pair(dst + 16384, tm, full0, 64 * (int)rank, row0, bh);
+          } else {
+            mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kTileA);
+            for (int hh = 0; hh < KH; ++hh) tma_load_3d(dst + hh * 16384, tm, &bars.ring_full[st], hh * 64, row0, bh);
+          }
         }
         ++pos;
         return true;
@@ -296,11 +303,16 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           // the tile's first key / value slab does not depend on the operand buffers: fetch it before waiting for them
           alive = load_stage(tmKc, tmKcH, c0 * kBC, bh);
           if (alive) alive = load_stage(tmVc, tmVcH, c0 * kBC, bh);
-          if (!alive || !mbar_wait_x<PAIR>(&bars.a_free, (xt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
-          mbar_arrive_expect_tx(&bars.xy_full, 2 * Cfg::kTileA);
-          for (int hh = 0; hh < KH; ++hh) {
-            tma_load_3d(smem + Cfg::kOffA + hh * 16384, tmX, &bars.xy_full, hh * 64, xt * 128, bh);
-            tma_load_3d(smem + Cfg::kOffA2 + hh * 16384, tmY, &bars.xy_full, hh * 64, xt * 128, bh);
+          if (!alive || !__all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.a_free, (xt_count & 1) ^ 1, abort_flag))) {
+            alive = false;
+            break;
+          }
+          if (leader) {
+            mbar_arrive_expect_tx(&bars.xy_full, 2 * Cfg::kTileA);
+            for (int hh = 0; hh < KH; ++hh) {
+              tma_load_3d(smem + Cfg::kOffA + hh * 16384, tmX, &bars.xy_full, hh * 64, xt * 128, bh);
+              tma_load_3d(smem + Cfg::kOffA2 + hh * 16384, tmY, &bars.xy_full, hh * 64, xt * 128, bh);
+            }
           }
           for (int c = c0 + 1; c < c0 + ncs && alive; ++c) {
             alive = load_stage(tmKc, tmKcH, c * kBC, bh);

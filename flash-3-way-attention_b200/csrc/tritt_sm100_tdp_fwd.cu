@@ -192,18 +192,24 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      tma_prefetch_desc(&tmK1);
-      tma_prefetch_desc(&tmK2);
-      tma_prefetch_desc(&tmSV1);
+    // (the whole warp walks the schedule converged, one elected lane issues the copies)
+    {
+      const bool leader = elect_one();
+      if (leader) {
+        tma_prefetch_desc(&tmK1);
+        tma_prefetch_desc(&tmK2);
+        tma_prefetch_desc(&tmSV1);
+      }
       uint32_t kt_count = 0, pos = 0;
       bool alive = true;
       auto load_stage = [&](const CUtensorMap* tm, int row0, int bh) -> bool {
         const int st = pos % NS;
-        if (!mbar_wait(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag)) return false;
-        mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kTileA);
-        for (int hh = 0; hh < KH; ++hh)
-          tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kTileA + hh * 16384, tm, &bars.ring_full[st], hh * 64, row0, bh);
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars.ring_empty[st], ((pos / NS) & 1) ^ 1, abort_flag))) return false;
+        if (leader) {
+          mbar_arrive_expect_tx(&bars.ring_full[st], Cfg::kTileA);
+          for (int hh = 0; hh < KH; ++hh)
+            tma_load_3d(smem + Cfg::kOffRing + st * Cfg::kTileA + hh * 16384, tm, &bars.ring_full[st], hh * 64, row0, bh);
+        }
         ++pos;
         return true;
       };
@@ -216,10 +222,15 @@ tdp_fwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           j_range(qa, qb, kt, jt0, njt);
           // the first K1 tile does not depend on the previous k-tile: fetch it before waiting for the operand buffer
           alive = load_stage(&tmK1, jt0 * kBJ, bh);
-          if (!alive || !mbar_wait(&bars.a_free, (kt_count & 1) ^ 1, abort_flag)) { alive = false; break; }
-          mbar_arrive_expect_tx(&bars.k2_full, Cfg::kTileA);
-          for (int hh = 0; hh < KH; ++hh)
-            tma_load_3d(smem + Cfg::kOffAa + hh * 16384, &tmK2, &bars.k2_full, hh * 64, kt * 128, bh);
+          if (!alive || !__all_sync(0xffffffffu, mbar_wait(&bars.a_free, (kt_count & 1) ^ 1, abort_flag))) {
+            alive = false;
+            break;
+          }
+          if (leader) {
+            mbar_arrive_expect_tx(&bars.k2_full, Cfg::kTileA);
+            for (int hh = 0; hh < KH; ++hh)
+              tma_load_3d(smem + Cfg::kOffAa + hh * 16384, &tmK2, &bars.k2_full, hh * 64, kt * 128, bh);
+          }
           // ring order: K1(0), V(0), K1(1), V(1), ...
           for (int jt = jt0; jt < jt0 + njt && alive; ++jt) {
             alive = load_stage(&tmSV1, jt * kBJ, bh);
