@@ -162,7 +162,16 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmOwn0, const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (the whole warp walks the schedule converged and one elected lane issues: the descriptor arithmetic stays on
+    //  the uniform datapath)
+    {
+      const bool leader = elect_one();
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (leader) mma_commit(bar);
+      };
       constexpr int kFmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = make_idesc_f16(128, 128, kFmt, false, false);
       constexpr uint32_t idesc_acc = make_idesc_f16(128, D, kFmt, false, true);
@@ -176,14 +185,14 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmOwn0, const __grid_c
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-          mma_ss_lo(tmem + Cfg::kTmemS, own0 + kk, b0 + kk, kHi, idesc_s, k > 0);
+          if (leader) mma_ss_lo(tmem + Cfg::kTmemS, own0 + kk, b0 + kk, kHi, idesc_s, k > 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-          mma_ss_lo(tmem + Cfg::kTmemDP, own1 + kk, b1 + kk, kHi, idesc_s, k > 0);
+          if (leader) mma_ss_lo(tmem + Cfg::kTmemDP, own1 + kk, b1 + kk, kHi, idesc_s, k > 0);
         }
-        mma_commit(&bars.sd_ready);
+        commit(&bars.sd_ready);
       };
       // accumulations with the 16-bit P / dS read from TMEM and the ring tiles used row-major
       auto issue_acc = [&](int st, uint32_t acc) {
@@ -193,37 +202,40 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmOwn0, const __grid_c
           // d_vc += P^T * dOut,  d_kc += dS^T * X
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            mma_ts_lo(tmem + Cfg::kTmemAcc0, tmem + Cfg::kTmemS + k * 8, m1 + k * (2048 >> 4), kHi, idesc_acc,
-                      k > 0 ? 1u : acc);
+            if (leader)
+              mma_ts_lo(tmem + Cfg::kTmemAcc0, tmem + Cfg::kTmemS + k * 8, m1 + k * (2048 >> 4), kHi, idesc_acc,
+                        k > 0 ? 1u : acc);
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            mma_ts_lo(tmem + Cfg::kTmemAcc1, tmem + Cfg::kTmemDP + k * 8, m0 + k * (2048 >> 4), kHi, idesc_acc,
-                      k > 0 ? 1u : acc);
+            if (leader)
+              mma_ts_lo(tmem + Cfg::kTmemAcc1, tmem + Cfg::kTmemDP + k * 8, m0 + k * (2048 >> 4), kHi, idesc_acc,
+                        k > 0 ? 1u : acc);
         } else {
           // d_rows += dS * K
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            mma_ts_lo(tmem + Cfg::kTmemAcc0, tmem + Cfg::kTmemDP + k * 8, m0 + k * (2048 >> 4), kHi, idesc_acc,
-                      k > 0 ? 1u : acc);
+            if (leader)
+              mma_ts_lo(tmem + Cfg::kTmemAcc0, tmem + Cfg::kTmemDP + k * 8, m0 + k * (2048 >> 4), kHi, idesc_acc,
+                        k > 0 ? 1u : acc);
         }
       };
-      bool alive = mbar_wait(&bars.own_full, 0, abort_flag) && mbar_wait(&bars.ring_full[0], 0, abort_flag);
+      bool alive = wait_all(&bars.own_full, 0) && wait_all(&bars.ring_full[0], 0);
       if (alive) {
         tc_fence_after();
         issue_sd(0);
       }
       for (int i = 0; i < n_t && alive; ++i) {
         const int st = i % NS;
-        if (!mbar_wait(&bars.pd_ready, i & 1, abort_flag)) { alive = false; break; }
+        if (!wait_all(&bars.pd_ready, i & 1)) { alive = false; break; }
         tc_fence_after();
         issue_acc(st, i > 0);
-        mma_commit(&bars.ring_empty[st]);
+        commit(&bars.ring_empty[st]);
         if (i + 1 < n_t) {
-          if (!mbar_wait(&bars.ring_full[(i + 1) % NS], ((i + 1) / NS) & 1, abort_flag)) { alive = false; break; }
+          if (!wait_all(&bars.ring_full[(i + 1) % NS], ((i + 1) / NS) & 1)) { alive = false; break; }
           tc_fence_after();
           issue_sd((i + 1) % NS);  // (overwrites P / dS of tile i: the pipe runs it after the products above)
         } else {
-          mma_commit(&bars.acc_done);
+          commit(&bars.acc_done);
         }
       }
     }

@@ -145,7 +145,16 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (the whole warp walks the schedule converged and one elected lane issues: the descriptor arithmetic stays on
+    //  the uniform datapath)
+    {
+      const bool leader = elect_one();
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (leader) mma_commit(bar);
+      };
       constexpr int kFmt = std::is_same<T16, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = make_idesc_f16(128, 128, kFmt, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, D, kFmt, false, true);
@@ -156,34 +165,34 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t kk = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-          mma_ss_lo(tmem, xLo + kk, bLo + kk, kHi, idesc_s, k > 0);
+          if (leader) mma_ss_lo(tmem, xLo + kk, bLo + kk, kHi, idesc_s, k > 0);
         }
-        mma_commit(&bars.s_ready);
+        commit(&bars.s_ready);
       };
       auto issue_pv = [&](int st, uint32_t acc) {
         // value tile used row-major: 64-column blocks 16 KiB apart, 16 rows (one instruction) 2 KiB apart
         const uint32_t bLo = desc_lo(smem_u32(smem + Cfg::kOffRing + st * 2 * Cfg::kTile + Cfg::kTile), 16384);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          mma_ts_lo(tmem + Cfg::kTmemO, tmem + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv, k > 0 ? 1u : acc);
+          if (leader) mma_ts_lo(tmem + Cfg::kTmemO, tmem + k * 8, bLo + k * (2048 >> 4), kHi, idesc_pv, k > 0 ? 1u : acc);
       };
-      bool alive = mbar_wait(&bars.x_full, 0, abort_flag) && mbar_wait(&bars.ring_full[0], 0, abort_flag);
+      bool alive = wait_all(&bars.x_full, 0) && wait_all(&bars.ring_full[0], 0);
       if (alive) {
         tc_fence_after();
         issue_s(0);
       }
       for (int i = 0; i < n_ct && alive; ++i) {
         const int st = i % NS;
-        if (!mbar_wait(&bars.p_ready, i & 1, abort_flag)) { alive = false; break; }
+        if (!wait_all(&bars.p_ready, i & 1)) { alive = false; break; }
         tc_fence_after();
         issue_pv(st, i > 0);
-        mma_commit(&bars.ring_empty[st]);
+        commit(&bars.ring_empty[st]);
         if (i + 1 < n_ct) {
-          if (!mbar_wait(&bars.ring_full[(i + 1) % NS], ((i + 1) / NS) & 1, abort_flag)) { alive = false; break; }
+          if (!wait_all(&bars.ring_full[(i + 1) % NS], ((i + 1) / NS) & 1)) { alive = false; break; }
           tc_fence_after();
           issue_s((i + 1) % NS);   // (overwrites P(i): the pipe runs it after P(i)*V(i), issued just above)
         } else {
-          mma_commit(&bars.o_done);
+          commit(&bars.o_done);
         }
       }
     }
