@@ -48,7 +48,9 @@ constexpr int kBC = 128;  // key columns per slab
 
 template <int D> struct BwdCfg {
   static constexpr int kTileA = 128 * D * 2;   // one 128-row operand / key / value tile
-  static constexpr int kStages = 4;            // ring of column tiles: Kc(c), Vc(c), Kc(c+1), Vc(c+1)
+  // ring of column tiles Kc(c), Vc(c), Kc(c+1), Vc(c+1), ...: two slabs deep at head dimension 128 (all the shared
+  // memory there is), four at 64
+  static constexpr int kStages = D == 64 ? 8 : 4;
   static constexpr int kOffA = 0;              // A  (row-key pre-product)
   static constexpr int kOffA2 = kTileA;        // A' (row-value pre-product)
   static constexpr int kOffRing = 2 * kTileA;
@@ -58,8 +60,9 @@ template <int D> struct BwdCfg {
   static constexpr int kOffVec = kOffDq + D * 4;                 // [2 parities][2][D] fp32: Q[q], dO[q]
   static constexpr int kOffMisc = kOffVec + 4 * D * 4;           // [4] fp32: Dq partials
   static constexpr int kOffBars = kOffMisc + 16;                 // barriers (no static shared memory is used, so
-  static constexpr int kSmem = kOffBars + 208;                   //  the dynamic region starts 1024-byte aligned)
+  static constexpr int kSmem = kOffBars + 288;                   //  the dynamic region starts 1024-byte aligned)
   static constexpr int kTmemS = 0, kTmemDP = 128, kTmemG = 256, kTmemU = 256 + D;
+  static constexpr int kTmemP = 384;   // head dimension 64 only: two buffers of 64 columns for P (by slab parity)
 };
 
 // NSW soft-max warpgroups (2 or 4) + 4 service warps (TMA, MMA, 2 idle) + the fold warpgroup
@@ -81,9 +84,14 @@ struct BwdParams {
 };
 
 struct BwdBarriers {
-  uint64_t ring_full[4], ring_empty[4];
+  uint64_t ring_full[8], ring_empty[8];
   uint64_t xy_full, ax_ready, ay_ready, a_free;  // A (score operand) and A' (dP operand) become ready separately
-  uint64_t s_ready, dp_ready, p_ready[2], ds_ready;  // slab hand-offs (P in two column halves)
+  uint64_t s_ready, dp_ready, ds_ready;              // slab hand-offs
+  // P in two column halves, a pair of barriers per slab parity: with the early score product the soft-max warps
+  // can hand over P(c+1) before the issuing warp has looked at P(c) (it may be waiting for the fold at a tile's
+  // first slab), and a barrier that is two phases ahead of its waiter reads as not ready for ever
+  uint64_t p_ready[2][2];
+  uint64_t s_free;                                   // head dimension 64: the soft-max warps hold a slab's scores in registers
   uint64_t gu_done, u_free, g_free;               // tile hand-offs with the fold warpgroup (U is drained first)
   uint64_t sm_sync, fold_sync;
   uint64_t vec_free[2];                           // fold warpgroup -> soft-max: a copy of Q[q] / dO[q] is no longer read
@@ -130,8 +138,13 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
   constexpr int kNumSoftmax = BwdThreads<NSW>::kSoftmax;
   constexpr int kFoldWarp0 = BwdThreads<NSW>::kFoldWarp0;
   constexpr int CW = kBC / NSW;  // slab columns owned by one soft-max warpgroup
+  // Head dimension 64 leaves 128 columns of tensor memory free: P then goes to a buffer of its own (two, by slab
+  // parity) instead of over the scores, and the next slab's score product is issued as soon as the soft-max warps hold
+  // this slab's scores in registers (`s_free`) instead of after U has consumed P: the loop S -> P -> U -> S is open.
+  // (U(c) is issued before S(c+2), and the pipe runs in order, so P(c) has been consumed when P(c+2) is written.)
+  constexpr bool kFreeS = D == 64 && !PAIR;
   extern __shared__ __align__(1024) uint8_t smem[];
-  static_assert(sizeof(BwdBarriers) <= 208, "barrier block too large");
+  static_assert(sizeof(BwdBarriers) <= 288, "barrier block too large");
   BwdBarriers& bars = *reinterpret_cast<BwdBarriers*>(smem + Cfg::kOffBars);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (smem_u32(smem) & 1023u) {
@@ -155,9 +168,9 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
     mbar_init(&bars.a_free, 1);   // a commit behind the tile's last score / dP products
     mbar_init(&bars.s_ready, 1);
     mbar_init(&bars.dp_ready, 1);
-    mbar_init(&bars.p_ready[0], kToMmaSm);
-    mbar_init(&bars.p_ready[1], kToMmaSm);
+    for (int i = 0; i < 4; ++i) mbar_init(&bars.p_ready[i >> 1][i & 1], kToMmaSm);
     mbar_init(&bars.ds_ready, kToMmaSm);
+    mbar_init(&bars.s_free, kToMmaSm);
     mbar_init(&bars.gu_done, 1);
     mbar_init(&bars.u_free, kToMmaFold);
     mbar_init(&bars.g_free, kToMmaFold);
@@ -399,13 +412,14 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
       constexpr int KPW = CW / 16;  // 16-deep MMA steps per warpgroup
       // U is issued in two halves: the k-steps fed by the first half of every warpgroup's columns as soon as
       // that half of P is there, the rest when the second half arrives (same accumulation chain).
-      auto issue_u_half = [&](uint32_t pos, uint32_t acc, int half) {
+      auto issue_u_half = [&](uint32_t pos, uint32_t acc, int half, uint32_t pbuf) {
         const uint32_t st = pos % NS;
         bool first = half == 0;
 #pragma unroll
         for (int k = 0; k < kBC / 16; ++k) {
           if (((k % KPW) >= KPW / 2) != (half == 1)) continue;
-          const uint32_t a = tmem + Cfg::kTmemS + (k / KPW) * CW + (k % KPW) * 8;
+          const uint32_t a = kFreeS ? tmem + Cfg::kTmemP + pbuf * 64 + k * 8
+                                    : tmem + Cfg::kTmemS + (k / KPW) * CW + (k % KPW) * 8;
           mma_ts_any(tmem + Cfg::kTmemU, a, ringMN + st * kTile16 + k * (2048 >> 4), idesc_g, first ? acc : 1u);
           first = false;
         }
@@ -441,17 +455,24 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           if (ncs == 1) commit(&bars.a_free);
           for (int c = 0; c < ncs && alive; ++c, ++n) {
             const bool more = c + 1 < ncs;
-            if (!wait_all(&bars.p_ready[0], n & 1)) { alive = false; break; }
+            if constexpr (kFreeS) {
+              if (!wait_all(&bars.s_free, n & 1)) { alive = false; break; }
+              tc_fence_after();
+              if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
+            }
+            if (!wait_all(&bars.p_ready[n & 1][0], (n >> 1) & 1)) { alive = false; break; }
             if (c == 0) {
               // the fold warpgroup must have drained the previous tile's U
               if (!wait_all(&bars.u_free, (xt_count & 1) ^ 1)) { alive = false; break; }
             }
             tc_fence_after();
-            issue_u_half(base + 2 * c + 1, c > 0, 0);
-            if (!wait_all(&bars.p_ready[1], n & 1)) { alive = false; break; }
+            issue_u_half(base + 2 * c + 1, c > 0, 0, n & 1);
+            if (!wait_all(&bars.p_ready[n & 1][1], (n >> 1) & 1)) { alive = false; break; }
             tc_fence_after();
-            issue_u_half(base + 2 * c + 1, c > 0, 1);
-            if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
+            issue_u_half(base + 2 * c + 1, c > 0, 1, n & 1);
+            if constexpr (!kFreeS) {
+              if (more && !issue_s(base + 2 * (c + 1))) { alive = false; break; }
+            }
             if (!wait_all(&bars.ds_ready, n & 1)) { alive = false; break; }
             if (c == 0) {
               // ... and the previous tile's G
@@ -587,7 +608,14 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
           tmem_ld32(tS + 32, sh[1]);
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
-            if (hf == 1) tmem_wait_ld();
+            if (hf == 1) {
+              tmem_wait_ld();
+              if constexpr (kFreeS) {
+                // both halves of the scores are in registers: the next slab's product may overwrite them
+                tc_fence_before();
+                to_mma(&bars.s_free);
+              }
+            }
             const uint32_t(&s)[32] = sh[hf];
             const int l2 = lo - hf * 32, h2 = hi - hf * 32;
             if (l2 <= 0 && h2 >= 31) {
@@ -606,10 +634,11 @@ tdp_bwd_kernel(const __grid_constant__ CUtensorMap tmK1, const __grid_constant__
               }
             }
             // P half -> S columns this thread has already read; hand it to the MMA warp right away
-            tmem_st16(tS + hf * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[hf * 16]));
+            tmem_st16(kFreeS ? tmem + lane_base + Cfg::kTmemP + (n & 1) * 64 + wg * 32 + hf * 16 : tS + hf * 16,
+                      *reinterpret_cast<uint32_t(*)[16]>(&pk[hf * 16]));
             tmem_wait_st();
             tc_fence_before();
-            to_mma(&bars.p_ready[hf]);
+            to_mma(&bars.p_ready[n & 1][hf]);
           }
           // ---- dP, P -> dS
           alive = __all_sync(0xffffffffu, mbar_wait_x<PAIR>(&bars.dp_ready, n & 1, abort_flag));
