@@ -30,6 +30,8 @@
 // bound part) overlap the tensor pipe although S and dP are single-buffered:
 //     MMA:      U(c) S(c+1) | G(c) dP(c+1) | U(c+1) S(c+2) | ...
 //     soft-max:      [S(c+1) -> P(c+1)]  [dP(c+1), P(c+1) -> dS(c+1)]
+// (At head dimension 64, where tensor memory has room, P has buffers of its own and S(c+1) goes before U(c): see
+// kFreeS in the kernel.)
 // The fold warpgroup drains G / U of tile t (TMEM -> registers -> shared memory -> TMA reduce-add)
 // while the other warps already run tile t+1.  Work item = (query, head, role); it walks the row tiles
 // x <= q and, inside, the column slabs c <= q.
